@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 10
+#define B200_ABI_VERSION 11
 
 enum {
   B200_OK = 0,
@@ -315,6 +315,11 @@ int b200_clamped_glu(const float* gate_up, void* out, int out_dtype, int T, int 
 int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, float* state,
                           const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                           void* out, int out_dtype, int T, int B, int C, int taps, void* stream);
+/* The same convolution with two more choices: in_bias fp32 [C] (or NULL) is added to every input read from `in` (the bias of
+ * the projection that produced it; the state keeps biased inputs), and silu == 0 leaves the convolution's sum as it is. */
+int b200_causal_conv(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, const float* in_bias, int silu,
+                     float* state, const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot,
+                     const int32_t* seq_pos0, void* out, int out_dtype, int T, int B, int C, int taps, void* stream);
 /* Selective state-space scan: xbc [T][C] = [x: H*P | B: G*N | C: G*N] (x_dtype); dt_raw = dt_in[t][dt_col0 + h] (fp32);
  * dt = softplus(dt_raw + dt_bias[h]); S = exp(-exp(A_log[h]) dt) S + dt B x^T; y = S^T C + D[h] x.
  * state fp32 [slots][H][P][N], updated; y fp32 [T][H*P].  Head h reads group h / (H / G).  N <= 256.
@@ -336,17 +341,35 @@ int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* 
  * q fp32 rows (pitch ldq, head h at column h * D); token t is position tok_pos[t] of the sequence whose block-table row is
  * tok_row[t] and sees keys j with 0 <= pos - j < window, all already in the pools.  Value rows have pitch v_pitch >= Dv
  * (v_pool may be k_pool itself, with the values in the leading columns of the key rows).  out [T][H][Dv] in kv_dtype.
- * Dv <= 512. */
+ * Dv <= 512.
+ * Variants: chunk > 0 also hides keys before the first position of the query's chunk, pos - pos % chunk; softcap > 0 replaces
+ * the scaled score s by softcap * tanh(s / softcap); sigmoid_bias fp32 [H] (or NULL) makes the weight of a visible key
+ * sigmoid(s + sigmoid_bias[h]) with no normalisation over keys (no sink then); v_div >= 1: key head g reads value head
+ * g / v_div of a value pool with G / v_div heads; out_f32: fp32 output rows whatever kv_dtype. */
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
-                       int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, void* stream);
+                       int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
+                       float softcap, const float* sigmoid_bias, int v_div, int out_f32, void* stream);
 /* The same attention for prompt portions on the tensor cores (bf16 pools; D and Dv multiples of 16, Dv <= 256, else
  * B200_ERR_UNSUPPORTED): sequence s brings tokens [seq_start[s], seq_start[s+1]) at positions seq_pos0[s].., block-table row
- * seq_slot[s]; max_new = the longest portion of the step.  q is rounded to bf16; softmax and accumulation are fp32. */
+ * seq_slot[s]; max_new = the longest portion of the step.  q is rounded to bf16; softmax and accumulation are fp32.
+ * chunk / softcap / sigmoid_bias / v_div / out_f32 as above; split_p: the weights enter the tensor cores as two bf16 terms
+ * (rounded value + remainder) instead of one. */
 int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
                                int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
-                               int Dv, int v_pitch, int block_size, void* stream);
+                               int Dv, int v_pitch, int block_size, int chunk, float softcap, const float* sigmoid_bias, int v_div,
+                               int out_f32, int split_p, void* stream);
+/* Between the projections and the attention of layers that norm and rotate: fp32 rows `src` (pitch ld) hold q [H][D] at
+ * q_col0, k [G][D] at k_col0, v [Gv][Dv] at v_col0.  q_norm / k_norm fp32 [H * D] / [G * D] (or NULL): RMS norm over the WHOLE
+ * projection, times the weight.  The first rot_n columns of every q and k head turn by tok_pos[t]: pairs (i, i + rot_n / 2) when
+ * rot_half, else (2i, 2i + 1); (u, v) -> (u cos - v sin, v cos + u sin), cos / sin fp32 tables [positions][rot_n / 2].
+ * q -> q_out fp32 [T][H * D]; k, v -> pools K [num_blocks][G][block_size][D], V [num_blocks][Gv][block_size][Dv] by slot. */
+int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0, int v_col0, const float* q_norm,
+                               const float* k_norm, float eps, int rot_n, int rot_half, const float* cos_table,
+                               const float* sin_table, const int32_t* tok_pos, const int64_t* slot_mapping, float* q_out,
+                               void* k_pool, void* v_pool, int kv_dtype, int T, int H, int G, int Gv, int D, int Dv, int block_size,
+                               void* stream);
 /* Router decision over fp32 logits [T] rows of pitch ld (+ bias fp32 [E] when given): the `top` largest (ties to the lower
  * index); weights = sigmoid of each chosen logit, no renormalisation (B200_ROUTE_SIGMOID), or the softmax over the chosen
  * logits only (B200_ROUTE_SOFTMAX_TOP). */
@@ -398,6 +421,20 @@ int b200_rmsnorm_cols(const float* in, int ld, int col0, int n, const float* w, 
 /* o fp32 [T][H][P]: out = o / sqrt(mean_P(o^2) + eps) * w[0..P) * silu(gate), gate = columns gate_col0.. of fp32 rows (pitch ldg) */
 int b200_head_rmsnorm_gate(const float* o, const float* gate, int ldg, int gate_col0, const float* w, float eps, void* out,
                            int out_dtype, int T, int H, int P, void* stream);
+/* Parallel-branch residual step with a grouped RMS norm: x[t] += y1[t] + y2[t] (fp32 rows of pitch ld1 / ld2; y2 or both may be
+ * NULL); out[t] (or NULL) = x[t] cut into `groups` equal consecutive parts, each divided by its own sqrt(mean(part^2) + eps), the
+ * whole times w.  x fp32 [T][W]. */
+int b200_add_group_rmsnorm(float* x, const float* y1, int ld1, const float* y2, int ld2, const float* w, int groups, float eps,
+                           void* out, int out_dtype, int T, int W, void* stream);
+/* out[t][0..n) = a N(z) + b N(z^2) + c N(z^3) + e with elementwise powers, N(u) = u / sqrt(mean(u^2) + eps) over the n columns,
+ * z = columns [col0, col0 + n) of the fp32 rows `in` (pitch ld), coef = {a, b, c, e} fp32 on the device */
+int b200_poly_norm(const float* in, int ld, int col0, int n, const float* coef, float eps, void* out, int out_dtype, int ldo, int T,
+                   void* stream);
+/* Differential attention, closing step: a fp32 [T][2 H][P], the kv group of `rep` output heads storing its first maps in rows
+ * [2 rep g, 2 rep g + rep) and its second maps in the next rep rows.  o = a1 - lambda a2;
+ * out[t][h] = o / sqrt(mean_P(o^2) + eps) * post * sigmoid(gate[t * ldg + gate_col0 + h]) (gate NULL: no gate). */
+int b200_diff_head_norm_gate(const float* a, float lambda, float post, const float* gate, int ldg, int gate_col0, float eps,
+                             void* out, int out_dtype, int T, int H, int rep, int P, void* stream);
 /* gate_up fp32 [T][2 ff] (gate first): out = act(gate) * up, act = B200_ACT_SILU or B200_ACT_GELU_TANH */
 int b200_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, int act, void* stream);
 /* Gated delta rule, preparation: qkv fp32 rows [q: G*D | k: G*D | v: H*P] (pitch ldc) are the convolved activations; q and k

@@ -128,6 +128,91 @@ __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const floa
   for (int i = lane; i < P; i += 32) stf(out, wid * P + i, r[i] * inv * w[i] * silu_f(gr[i]));
 }
 
+// Parallel-branch residual step: x[t] += y1[t] + y2[t] (either may be absent), then out[t] = the GROUPED RMS norm of x[t]
+// times w: the row is cut into `groups` equal consecutive parts and each part is divided by its own sqrt(mean(part^2) + eps).
+// One CTA per token, the row in shared memory; warps take the groups round-robin, so the sums do not depend on the batch.
+template <typename OT>
+__global__ void add_group_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y1, int ld1, const float* __restrict__ y2,
+                                         int ld2, const float* __restrict__ w, int groups, float eps, OT* __restrict__ out, int W) {
+  griddep_launch();
+  griddep_wait();
+  extern __shared__ float row[];  // [W] the row, [groups] 1 / rms per group
+  float* inv = row + W;
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float r = x[(int64_t)t * W + i];
+    if (y1) r += y2 ? y1[(int64_t)t * ld1 + i] + y2[(int64_t)t * ld2 + i] : y1[(int64_t)t * ld1 + i];
+    row[i] = r;
+    if (y1) x[(int64_t)t * W + i] = r;
+  }
+  __syncthreads();
+  if (!out) return;
+  const int gs = W / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int g = warp; g < groups; g += blockDim.x >> 5) {
+    float ss = 0.f;
+    for (int i = lane; i < gs; i += 32) ss += row[g * gs + i] * row[g * gs + i];
+    ss = warp_sum(ss);
+    if (lane == 0) inv[g] = 1.0f / sqrtf(ss / (float)gs + eps);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < W; i += blockDim.x) stf(out, (int64_t)t * W + i, row[i] * inv[i / gs] * w[i]);
+}
+
+// Polynomial activation with unit-RMS powers: out = a N(z) + b N(z^2) + c N(z^3) + e, powers elementwise, N(u) = u / sqrt(mean(u^2)
+// + eps) over the n columns of the token; coef = {a, b, c, e} on the device.  z = columns [col0, col0 + n) of fp32 rows.
+template <typename OT>
+__global__ void poly_norm_kernel(const float* __restrict__ in, int ld, int col0, int n, const float* __restrict__ coef, float eps,
+                                 OT* __restrict__ out, int ldo) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* r = in + (int64_t)t * ld + col0;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float z2 = r[i] * r[i];
+    s2 += z2;
+    s4 += z2 * z2;
+    s6 += z2 * z2 * z2;
+  }
+  s2 = block_sum(s2, red);
+  s4 = block_sum(s4, red);
+  s6 = block_sum(s6, red);
+  const float a = coef[0] / sqrtf(s2 / (float)n + eps), b = coef[1] / sqrtf(s4 / (float)n + eps),
+              c = coef[2] / sqrtf(s6 / (float)n + eps), e = coef[3];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float z = r[i];
+    stf(out, (int64_t)t * ldo + i, a * z + b * (z * z) + c * (z * z * z) + e);
+  }
+}
+
+// Differential attention, closing step.  a fp32 [T][2 H][P] holds both maps' outputs: the kv group of `rep` output heads
+// stores its first maps in rows [2 rep g, 2 rep g + rep) and its second maps in the next rep rows.  One warp per (token,
+// output head): o = a1 - lambda a2;  out = o / sqrt(mean_P(o^2) + eps) * post * sigmoid(gate[h]).
+template <typename OT>
+__global__ void diff_head_norm_gate_kernel(const float* __restrict__ a, float lambda, float post, const float* __restrict__ gate,
+                                           int ldg, int gcol0, float eps, OT* __restrict__ out, int T, int H, int rep, int P) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (int64_t)T * H) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = wid / H;
+  const int h = (int)(wid - t * H);
+  const int g = h / rep, j = h - g * rep;
+  const float* a1 = a + ((t * 2 * H) + 2 * rep * g + j) * P;
+  const float* a2 = a1 + (int64_t)rep * P;
+  float ss = 0.f;
+  for (int i = lane; i < P; i += 32) {
+    const float o = a1[i] - lambda * a2[i];
+    ss += o * o;
+  }
+  ss = warp_sum(ss);
+  float f = post / sqrtf(ss / (float)P + eps);
+  if (gate) f *= 1.0f / (1.0f + expf(-gate[t * ldg + gcol0 + h]));
+  for (int i = lane; i < P; i += 32) stf(out, wid * P + i, (a1[i] - lambda * a2[i]) * f);
+}
+
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -211,6 +296,44 @@ int b200_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, int 
   B200_DISPATCH_ELEM(out_dtype, OT,
                      B200_CUDA_OK(launch_kernel(glu_kernel<OT>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, gate_up,
                                                 (OT*)out, ff, act, total)));
+  return B200_OK;
+}
+
+int b200_add_group_rmsnorm(float* x, const float* y1, int ld1, const float* y2, int ld2, const float* w, int groups, float eps,
+                           void* out, int out_dtype, int T, int W, void* stream) {
+  B200_REQUIRE(x && (out == nullptr || w) && (y1 || !y2), "add_group_rmsnorm: null pointer");
+  B200_REQUIRE(groups >= 1 && W % groups == 0, "add_group_rmsnorm: rows of %d do not split into %d equal groups", W, groups);
+  B200_REQUIRE((size_t)(W + groups) * 4 <= 200 * 1024, "add_group_rmsnorm: rows of %d do not fit shared memory", W);
+  if (T <= 0) return B200_OK;
+  const size_t smem = (size_t)(W + groups) * 4;
+  B200_DISPATCH_ELEM(out_dtype, OT, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(add_group_rmsnorm_kernel<OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_OK(launch_kernel(add_group_rmsnorm_kernel<OT>, dim3(T), dim3(256), smem, (cudaStream_t)stream, x, y1, ld1, y2, ld2, w,
+                               groups, eps, (OT*)out, W));
+  });
+  return B200_OK;
+}
+
+int b200_poly_norm(const float* in, int ld, int col0, int n, const float* coef, float eps, void* out, int out_dtype, int ldo, int T,
+                   void* stream) {
+  B200_REQUIRE(in && coef && out && n >= 1 && ldo >= n, "poly_norm: null pointer or bad shape");
+  if (T <= 0) return B200_OK;
+  B200_DISPATCH_ELEM(out_dtype, OT,
+                     B200_CUDA_OK(launch_kernel(poly_norm_kernel<OT>, dim3(T), dim3(n >= 1024 ? 256 : 128), 0, (cudaStream_t)stream,
+                                                in, ld, col0, n, coef, eps, (OT*)out, ldo)));
+  return B200_OK;
+}
+
+int b200_diff_head_norm_gate(const float* a, float lambda, float post, const float* gate, int ldg, int gate_col0, float eps,
+                             void* out, int out_dtype, int T, int H, int rep, int P, void* stream) {
+  B200_REQUIRE(a && out && H >= 1 && P >= 1 && rep >= 1 && H % rep == 0, "diff_head_norm_gate: null pointer or bad shape");
+  if (T <= 0) return B200_OK;
+  const int64_t warps = (int64_t)T * H;
+  B200_DISPATCH_ELEM(out_dtype, OT,
+                     B200_CUDA_OK(launch_kernel(diff_head_norm_gate_kernel<OT>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0,
+                                                (cudaStream_t)stream, a, lambda, post, gate, ldg, gate_col0, eps, (OT*)out, T, H, rep,
+                                                P)));
   return B200_OK;
 }
 

@@ -13,10 +13,12 @@ namespace b200 {
 constexpr int CONV_MAX_TAPS = 16;
 constexpr int CONV_RUN = 16;  // most consecutive tokens per thread (large steps): the window's earlier inputs and the taps are cache hits
 
-// one thread per (run of `run` tokens, channel); run = 1 for decode-sized steps
+// one thread per (run of `run` tokens, channel); run = 1 for decode-sized steps.  in_bias (or NULL) is added to every input
+// taken from `in` (a projection's bias: the state rows hold biased inputs already); silu == 0 leaves the sum as it is.
 template <typename OT>
 __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ cw,
-                                        const float* __restrict__ cb, const float* __restrict__ state,
+                                        const float* __restrict__ cb, const float* __restrict__ in_bias, int silu,
+                                        const float* __restrict__ state,
                                         const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_start,
                                         const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos0,
                                         OT* __restrict__ out, int T, int C, int taps, int run) {
@@ -25,6 +27,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld, in
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const float bias = cb ? cb[c] : 0.f;
+  const float ib = in_bias ? in_bias[c] : 0.f;
   const float* wc = cw + (int64_t)c * taps;
   const int t_end = min(T, (int)(blockIdx.y + 1) * run);
   for (int t = blockIdx.y * run; t < t_end; ++t) {
@@ -37,20 +40,21 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld, in
       const int src = i - (taps - 1 - j);  // portion index of the input under tap j (last tap = current token)
       float v;
       if (src >= 0)
-        v = in[(int64_t)(t - (taps - 1 - j)) * ld + col0 + c];
+        v = in[(int64_t)(t - (taps - 1 - j)) * ld + col0 + c] + ib;
       else if (has_state)
         v = st[(int64_t)(src + taps - 1) * C + c];
       else
         v = 0.f;
       acc += v * wc[j];
     }
-    stf(out, (int64_t)t * C + c, silu_f(acc));
+    stf(out, (int64_t)t * C + c, silu ? silu_f(acc) : acc);
   }
 }
 
 // new state = the last (taps - 1) inputs of [old state | this step's inputs]; one thread per (sequence, channel) reads
 // everything it needs before it writes, so the update is in place.  Runs after causal_conv_silu_kernel on the stream.
-__global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, int col0, float* __restrict__ state,
+__global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ in_bias,
+                                         float* __restrict__ state,
                                          const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                                          const int32_t* __restrict__ seq_pos0, int C, int taps) {
   griddep_launch();
@@ -67,7 +71,7 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, i
       const int i = n - (taps - 1) + k;  // portion index of what slot k must hold afterwards
       float v = 0.f;
       if (i >= 0)
-        v = in[(int64_t)(t0 + i) * ld + col0 + c];
+        v = in[(int64_t)(t0 + i) * ld + col0 + c] + (in_bias ? in_bias[c] : 0.f);
       else if (pos0 > 0)
         v = st[(int64_t)(i + taps - 1) * C + c];
       keep[k] = v;
@@ -330,22 +334,29 @@ using namespace b200;
 
 extern "C" {
 
-int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, float* state,
-                          const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
-                          void* out, int out_dtype, int T, int B, int C, int taps, void* stream) {
-  B200_REQUIRE(in && conv_w && state && tok_seq && seq_start && seq_slot && seq_pos0 && out, "causal_conv_silu: null pointer");
-  B200_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv_silu: %d taps (1..%d supported)", taps, CONV_MAX_TAPS);
+int b200_causal_conv(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, const float* in_bias, int silu,
+                     float* state, const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot,
+                     const int32_t* seq_pos0, void* out, int out_dtype, int T, int B, int C, int taps, void* stream) {
+  B200_REQUIRE(in && conv_w && state && tok_seq && seq_start && seq_slot && seq_pos0 && out, "causal_conv: null pointer");
+  B200_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: %d taps (1..%d supported)", taps, CONV_MAX_TAPS);
   if (T <= 0 || B <= 0) return B200_OK;
   const int th = 128;
   const int run = T / 256 < 1 ? 1 : T / 256 > CONV_RUN ? CONV_RUN : T / 256;
   B200_DISPATCH_ELEM(out_dtype, OT,
                      B200_CUDA_OK(launch_kernel(causal_conv_silu_kernel<OT>, dim3((C + th - 1) / th, (T + run - 1) / run), dim3(th), 0,
-                                                (cudaStream_t)stream, in, ld, col0, conv_w, conv_b, (const float*)state, tok_seq,
-                                                seq_start, seq_slot, seq_pos0, (OT*)out, T, C, taps, run)));
+                                                (cudaStream_t)stream, in, ld, col0, conv_w, conv_b, in_bias, silu, (const float*)state,
+                                                tok_seq, seq_start, seq_slot, seq_pos0, (OT*)out, T, C, taps, run)));
   if (taps > 1)
     B200_CUDA_OK(launch_kernel(conv_state_update_kernel, dim3((C + th - 1) / th, B), dim3(th), 0, (cudaStream_t)stream, in, ld,
-                               col0, state, seq_start, seq_slot, seq_pos0, C, taps));
+                               col0, in_bias, state, seq_start, seq_slot, seq_pos0, C, taps));
   return B200_OK;
+}
+
+int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, float* state,
+                          const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
+                          void* out, int out_dtype, int T, int B, int C, int taps, void* stream) {
+  return b200_causal_conv(in, ld, col0, conv_w, conv_b, nullptr, 1, state, tok_seq, seq_start, seq_slot, seq_pos0, out,
+                          out_dtype, T, B, C, taps, stream);
 }
 
 int b200_ssd_scan(const void* xbc, int x_dtype, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,

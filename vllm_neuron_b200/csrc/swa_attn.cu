@@ -8,6 +8,13 @@
 //     sink logit, running denominator = 1, accumulator = 0 -- the sink adds exp(sink) to the denominator once, has no key,
 //     no value, and is not multiplied by the score scale.
 //     Without a sink (sink == NULL) the softmax is the ordinary one over the visible keys.
+//     Variants of the same kernel, all parameters: keys confined to the query's CHUNK of positions (counted from position 0),
+//     a soft cap on the scaled score (cap tanh(s / cap)), SIGMOID weights sigmoid(s + bias[head]) that are not normalised
+//     over the keys (then no sink, no maximum, no denominator), several key heads sharing one value head (v_div: two score
+//     maps over the same values), and fp32 output rows;
+//   * qk_norm_rope_kv_write: the step between the projections (or their short convolutions) and the attention of layers
+//     that norm and rotate: an optional RMS norm over the WHOLE q (and k) projection, rotary positions from cos / sin tables
+//     on the leading columns of every head (pairs (i, i + n/2) or (2i, 2i + 1)), q to an fp32 buffer, k and v into the pools.
 // Pools: K [num_blocks][G][block_size][D], V [num_blocks][G][block_size][v_pitch] with values in the first Dv columns of a
 // row (v_pitch = Dv for a pool of its own; a value pool may alias the key pool, values = the leading columns of the key
 // rows, v_pitch = D: attention over cached latents).
@@ -38,6 +45,89 @@ __global__ void kv_write_vmix_kernel(const float* __restrict__ qkv, int ld, int 
     if (mode == 1) v_first[(int64_t)t * G * Dv + i] = v;
     if (mode == 2) v = (1.0f - lam) * v + lam * v_first[(int64_t)t * G * Dv + i];
     stf(v_pool, ((blk * G + g) * bs + off) * Dv + d, v);
+  }
+}
+
+// One CTA per token.  src fp32 rows hold q [H][D] at q_col0, k [G][D] at k_col0 and v [Gv][Dv] at v_col0.  q and k are
+// (optionally) divided by the RMS of their whole projection and multiplied by a weight per column, then the first rot_n
+// columns of every head turn by the token's position: column pairs (i, i + rot_n / 2) when rot_half, else (2i, 2i + 1); a pair
+// (u, v) becomes (u cos - v sin, v cos + u sin) with cos / sin from fp32 tables [positions][rot_n / 2] (any frequency
+// scaling and magnitude factor live in the tables).  q goes to q_out fp32 [T][H * D]; k and v to the pools by slot.
+template <typename KT>
+__global__ void qk_norm_rope_kv_write_kernel(const float* __restrict__ src, int ld, int q_col0, int k_col0, int v_col0,
+                                             const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                             int rot_n, int rot_half, const float* __restrict__ cos_t,
+                                             const float* __restrict__ sin_t, const int32_t* __restrict__ tok_pos,
+                                             const int64_t* __restrict__ slots, float* __restrict__ q_out, KT* __restrict__ k_pool,
+                                             KT* __restrict__ v_pool, int H, int G, int Gv, int D, int Dv, int bs) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ float red[2][33];
+  const int t = blockIdx.x;
+  const float* row = src + (int64_t)t * ld;
+  const int nq = H * D, nk = G * D;
+  float inv_q = 1.0f, inv_k = 1.0f;
+  if (q_norm || k_norm) {  // sums of squares over the whole projections
+    float sq = 0.f, sk = 0.f;
+    if (q_norm)
+      for (int i = threadIdx.x; i < nq; i += blockDim.x) sq += row[q_col0 + i] * row[q_col0 + i];
+    if (k_norm)
+      for (int i = threadIdx.x; i < nk; i += blockDim.x) sk += row[k_col0 + i] * row[k_col0 + i];
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if ((threadIdx.x & 31) == 0) {
+      red[0][threadIdx.x >> 5] = sq;
+      red[1][threadIdx.x >> 5] = sk;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int nw = (blockDim.x + 31) >> 5;
+      float a = threadIdx.x < nw ? red[0][threadIdx.x] : 0.f, b = threadIdx.x < nw ? red[1][threadIdx.x] : 0.f;
+      a = warp_sum(a);
+      b = warp_sum(b);
+      if (threadIdx.x == 0) {
+        red[0][32] = a;
+        red[1][32] = b;
+      }
+    }
+    __syncthreads();
+    if (q_norm) inv_q = 1.0f / sqrtf(red[0][32] / (float)nq + eps);
+    if (k_norm) inv_k = 1.0f / sqrtf(red[1][32] / (float)nk + eps);
+  }
+  const int pos = tok_pos[t];
+  const int half = rot_n >> 1;
+  const float* cs = cos_t + (int64_t)pos * half;
+  const float* sn = sin_t + (int64_t)pos * half;
+  const int64_t slot = slots[t];
+  const int64_t blk = slot / bs, off = slot % bs;
+  // the value of column i of a projection after its norm
+  auto turned = [&](int col0, const float* nw, float inv, int i) -> float {
+    const int d = i % D;
+    const float u = row[col0 + i] * (nw ? inv * nw[i] : 1.0f);
+    if (d >= rot_n) return u;
+    int partner, idx;
+    bool first;
+    if (rot_half) {
+      first = d < half;
+      idx = first ? d : d - half;
+      partner = first ? i + half : i - half;
+    } else {
+      first = (d & 1) == 0;
+      idx = d >> 1;
+      partner = i ^ 1;
+    }
+    const float o = row[col0 + partner] * (nw ? inv * nw[partner] : 1.0f);
+    return first ? u * cs[idx] - o * sn[idx] : u * cs[idx] + o * sn[idx];
+  };
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) q_out[(int64_t)t * nq + i] = turned(q_col0, q_norm, inv_q, i);
+  if (slot < 0) return;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int g = i / D, d = i - g * D;
+    stf(k_pool, ((blk * G + g) * bs + off) * D + d, turned(k_col0, k_norm, inv_k, i));
+  }
+  for (int i = threadIdx.x; i < Gv * Dv; i += blockDim.x) {
+    const int g = i / Dv, d = i - g * Dv;
+    stf(v_pool, ((blk * Gv + g) * bs + off) * Dv + d, row[v_col0 + i]);
   }
 }
 
@@ -125,7 +215,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     swa_sink_attn_kernel(const float* __restrict__ q, int ldq, const KT* __restrict__ k_pool, const KT* __restrict__ v_pool,
                          const int32_t* __restrict__ block_table, int64_t bt_stride, const int32_t* __restrict__ tok_row,
                          const int32_t* __restrict__ tok_pos, const float* __restrict__ sink, float scale, int window,
-                         KT* __restrict__ out, int T, int H, int G, int D, int Dv, int bs, int v_pitch) {
+                         void* __restrict__ out, int T, int H, int G, int D, int Dv, int bs, int v_pitch, int chunk, float softcap,
+                         const float* __restrict__ sig_bias, int v_div, int out_f32) {
   griddep_launch();
   griddep_wait();
   extern __shared__ __align__(16) float sm_att[];
@@ -137,6 +228,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   const int hb = H / QH;                          // head blocks per token
   const int t = blockIdx.x / hb, h0 = (blockIdx.x - t * hb) * QH;
   const int g = h0 / (H / G);                     // QH divides H / G: the block's heads share this kv head
+  const int Gv = G / v_div, gv = g / v_div;       // v_div key heads read one value head
+  const bool sig = sig_bias != nullptr;           // sigmoid weights: no maximum, no denominator
   for (int i = threadIdx.x; i < QH * D; i += ATT_WARPS * 32) {
     const int qh = i / D, d = i - qh * D;
     qs[qh * Dp + d] = q[(int64_t)t * ldq + (int64_t)(h0 + qh) * D + d];
@@ -144,13 +237,14 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   __syncthreads();
   const int pos = tok_pos[t];
   const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
-  const int lo = pos - window + 1 > 0 ? pos - window + 1 : 0;
+  int lo = pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (chunk > 0 && pos - pos % chunk > lo) lo = pos - pos % chunk;  // the first position of the query's chunk
   const bool vvec = (Dv & 1) == 0 && (v_pitch & 1) == 0;
   float m[QH], l[QH];  // the sink: exp(sink - m) = 1 in the denominator, nothing in the numerator
   float2 acc[QH][MAXC];
 #pragma unroll
   for (int qh = 0; qh < QH; ++qh) {
-    m[qh] = sink ? sink[h0 + qh] : -INFINITY;
+    m[qh] = sig ? 0.f : sink ? sink[h0 + qh] : -INFINITY;
     l[qh] = sink && warp == 0 ? 1.0f : 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) acc[qh][c] = make_float2(0.f, 0.f);
@@ -158,18 +252,25 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   for (int j0 = lo + 32 * warp; j0 <= pos; j0 += 32 * ATT_WARPS) {
     const int j = j0 + lane;
     const bool valid = j <= pos;
-    int64_t tile = 0;  // row index of (block, kv head, token) in the pools
+    int64_t tile = 0, vtile = 0;  // row index of (block, kv head, token) in the key / value pool
     float p[QH];
 #pragma unroll
     for (int qh = 0; qh < QH; ++qh) p[qh] = 0.f;
     if (valid) {
       const int64_t blk = bt[j / bs];
       tile = (blk * G + g) * bs + (j % bs);
+      vtile = (blk * Gv + gv) * bs + (j % bs);
       DotRows<KT, QH>::run(qs, Dp, k_pool + tile * D, D, p);
     }
 #pragma unroll
     for (int qh = 0; qh < QH; ++qh) {
-      const float s = valid ? p[qh] * scale : -INFINITY;
+      float s = p[qh] * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      if (sig) {
+        p[qh] = valid ? 1.0f / (1.0f + expf(-(s + sig_bias[h0 + qh]))) : 0.f;
+        continue;
+      }
+      if (!valid) s = -INFINITY;
       const float m_new = fmaxf(m[qh], warp_max(s));
       const float corr = expf(m[qh] - m_new);
       p[qh] = valid ? expf(s - m_new) : 0.f;
@@ -185,7 +286,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     // null page: finite values), so they add nothing
 #pragma unroll 8
     for (int jj = 0; jj < 32; ++jj) {
-      const int64_t tj = __shfl_sync(0xffffffffu, tile, jj);
+      const int64_t tj = __shfl_sync(0xffffffffu, vtile, jj);
       float pj[QH];
 #pragma unroll
       for (int qh = 0; qh < QH; ++qh) pj[qh] = __shfl_sync(0xffffffffu, p[qh], jj);
@@ -231,7 +332,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       lt += ml[2 * (w * QH + qh) + 1] * f;
       v += accs[((w * QH + qh) * MAXC + c) * 64 + e] * f;
     }
-    stf(out, ((int64_t)t * H + h0 + qh) * Dv + d, v / lt);
+    const float r = sig ? v : v / lt;
+    if (out_f32) reinterpret_cast<float*>(out)[((int64_t)t * H + h0 + qh) * Dv + d] = r;
+    else stf(reinterpret_cast<KT*>(out), ((int64_t)t * H + h0 + qh) * Dv + d, r);
   }
 }
 
@@ -254,13 +357,33 @@ int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* 
   return B200_OK;
 }
 
+int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0, int v_col0, const float* q_norm,
+                               const float* k_norm, float eps, int rot_n, int rot_half, const float* cos_table,
+                               const float* sin_table, const int32_t* tok_pos, const int64_t* slot_mapping, float* q_out,
+                               void* k_pool, void* v_pool, int kv_dtype, int T, int H, int G, int Gv, int D, int Dv, int block_size,
+                               void* stream) {
+  B200_REQUIRE(src && tok_pos && slot_mapping && q_out && k_pool && v_pool, "qk_norm_rope_kv_write: null pointer");
+  B200_REQUIRE(rot_n >= 0 && rot_n <= D && rot_n % 2 == 0 && (rot_n == 0 || (cos_table && sin_table)),
+               "qk_norm_rope_kv_write: %d rotating columns in heads of %d", rot_n, D);
+  B200_REQUIRE(H >= 1 && G >= 1 && Gv >= 1 && D >= 1 && Dv >= 1, "qk_norm_rope_kv_write: bad shape");
+  if (T <= 0) return B200_OK;
+  B200_DISPATCH_ELEM(kv_dtype, KT,
+                     B200_CUDA_OK(launch_kernel(qk_norm_rope_kv_write_kernel<KT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, src, ld,
+                                                q_col0, k_col0, v_col0, q_norm, k_norm, eps, rot_n, rot_half, cos_table, sin_table,
+                                                tok_pos, slot_mapping, q_out, (KT*)k_pool, (KT*)v_pool, H, G, Gv, D, Dv, block_size)));
+  return B200_OK;
+}
+
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
-                       int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, void* stream) {
+                       int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
+                       float softcap, const float* sigmoid_bias, int v_div, int out_f32, void* stream) {
   B200_REQUIRE(q && k_pool && v_pool && block_table && tok_row && tok_pos && out, "swa_sink_attn: null pointer");
   B200_REQUIRE(v_pitch >= Dv, "swa_sink_attn: value rows of pitch %d hold %d values", v_pitch, Dv);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "swa_sink_attn: %d query heads over %d kv heads", H, G);
-  B200_REQUIRE(window >= 1, "swa_sink_attn: window %d", window);
+  B200_REQUIRE(window >= 1 && chunk >= 0, "swa_sink_attn: window %d, chunk %d", window, chunk);
+  B200_REQUIRE(v_div >= 1 && G % v_div == 0, "swa_sink_attn: %d key heads do not share values %d by %d", G, v_div, v_div);
+  B200_REQUIRE(!(sigmoid_bias && sink), "swa_sink_attn: sigmoid weights have no denominator for a sink to join");
   B200_REQUIRE(Dv >= 1 && Dv <= 512 && D >= 1 && D <= 1024, "swa_sink_attn: head sizes %d / %d outside 1..1024 / 1..512", D, Dv);
   if (T <= 0) return B200_OK;
   B200_REQUIRE((int64_t)T * H < (1ll << 31), "swa_sink_attn: %d tokens x %d heads exceed the grid", T, H);
@@ -279,7 +402,7 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
                                         (int)smem));                                                                         \
     B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC, QH>, grid, dim3(ATT_WARPS * 32), smem, st, q, ldq,               \
                                (const KT*)k_pool, (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, \
-                               window, (KT*)out, T, H, G, D, Dv, block_size, v_pitch));                                               \
+                               window, out, T, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32));     \
   } while (0)
 #define ATT_LAUNCH(MC)                \
   do {                                \

@@ -7,6 +7,10 @@
 //   gathered page by page into shared memory with cp.async, one tile ahead of the MMAs (rows padded by 16 bytes:
 //   conflict-free ldmatrix), S = Q K^T and O += P V run
 //   on mma.sync m16n8k16 (bf16 in, fp32 accumulate); the mask is applied per element, the online softmax is fp32.
+// The variants of the warp kernel are parameters here too: a chunked mask, a soft cap on the scaled score, sigmoid weights with a
+// per-head bias (no maximum, no denominator), key heads that share a value head, fp32 output rows.  split_p keeps the weights'
+// precision through the tensor cores: P = hi + lo with hi = bf16(P), lo = bf16(P - hi), and O += hi V + lo V (the weights then
+// carry 16 mantissa bits instead of 8; the denominators are summed in fp32 either way).
 // Needs D % 16 == 0 and Dv % 16 == 0, Dv <= 256; other shapes, fp32 pools and decode-sized steps use the warp kernel.
 #include <math.h>
 
@@ -25,7 +29,8 @@ __global__ void __launch_bounds__(128)
                             const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                             const int32_t* __restrict__ seq_pos0, const float* __restrict__ sink, float scale, int window,
-                            __nv_bfloat16* __restrict__ out, int H, int G, int D, int Dv, int bs, int v_pitch) {
+                            void* __restrict__ out, int H, int G, int D, int Dv, int bs, int v_pitch, int chunk, float softcap,
+                            const float* __restrict__ sig_bias, int v_div, int out_f32, int split_p) {
   griddep_wait();
   const int sq = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * PF_ROWS;
   const int t0 = seq_start[sq], n = seq_start[sq + 1] - t0;
@@ -39,6 +44,9 @@ __global__ void __launch_bounds__(128)
   __nv_bfloat16* Vs0 = v_alias ? Ks0 : Ks0 + PF_STAGES * PF_KEYS * ldk;  // [PF_STAGES][32][ldv]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = h / (H / G);
+  const int Gv = G / v_div, gv = g / v_div;
+  const bool sig = sig_bias != nullptr;
+  const float sb = sig ? sig_bias[h] : 0.f;
   const int pos0 = seq_pos0[sq];
   const int32_t* bt = block_table + (int64_t)seq_slot[sq] * bt_stride;
   // ---- Q tile: fp32 rows -> bf16 shared memory (rows past the portion are zero)
@@ -52,7 +60,7 @@ __global__ void __launch_bounds__(128)
   const int r_lo = 16 * warp + (lane >> 2);
   const int p_lo = pos0 + i0 + r_lo, p_hi = p_lo + 8;
   const bool ok_lo = i0 + r_lo < n, ok_hi = i0 + r_lo + 8 < n;
-  float m_lo = sink ? sink[h] : -INFINITY, m_hi = m_lo;
+  float m_lo = sig ? 0.f : sink ? sink[h] : -INFINITY, m_hi = m_lo;
   float l_lo = sink && (lane & 3) == 0 ? 1.0f : 0.f, l_hi = l_lo;  // the sink's share of the denominator, counted once per row
   float o[2 * DV16M][4];
 #pragma unroll
@@ -61,7 +69,8 @@ __global__ void __launch_bounds__(128)
     for (int c = 0; c < 4; ++c) o[j][c] = 0.f;
   const int first_pos = pos0 + i0;
   const int last_row = (n - i0 < PF_ROWS ? n - i0 : PF_ROWS) - 1;
-  const int j_lo = first_pos - window + 1 > 0 ? first_pos - window + 1 : 0;
+  int j_lo = first_pos - window + 1 > 0 ? first_pos - window + 1 : 0;
+  if (chunk > 0 && first_pos - first_pos % chunk > j_lo) j_lo = first_pos - first_pos % chunk;
   const int j_hi = first_pos + last_row;  // inclusive
   const int kch = D / 8, vch = v_alias ? 0 : Dv / 8;  // 16-byte chunks per row
   // one tile of 32 keys (K and V rows, page by page through the block table) into stage `st`; rows past j_hi are zeros
@@ -72,9 +81,10 @@ __global__ void __launch_bounds__(128)
       const int r = i / (kch + vch), c = i - r * (kch + vch);
       const int j = j0 + r;
       const bool ok = j <= j_hi;
-      const int64_t row = ok ? ((int64_t)bt[j / bs] * G + g) * bs + (j % bs) : 0;
+      const int64_t blk = ok ? bt[j / bs] : 0;
+      const int64_t row = ok ? (blk * G + g) * bs + (j % bs) : 0, vrow = ok ? (blk * Gv + gv) * bs + (j % bs) : 0;
       if (c < kch) cp_async16(smem_u32(Kd + r * ldk + c * 8), k_pool + row * D + c * 8, ok);
-      else cp_async16(smem_u32(Vd + r * ldv + (c - kch) * 8), v_pool + row * v_pitch + (c - kch) * 8, ok);
+      else cp_async16(smem_u32(Vd + r * ldv + (c - kch) * 8), v_pool + vrow * v_pitch + (c - kch) * 8, ok);
     }
     cp_async_commit();  // an empty group past the last tile keeps the wait counts uniform
   };
@@ -116,8 +126,11 @@ __global__ void __launch_bounds__(128)
         const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
         const bool hi = c >= 2;
         const int pos = hi ? p_hi : p_lo;
-        const bool seen = (hi ? ok_hi : ok_lo) && key <= pos && pos - key < window;
-        const float v = seen ? s[j][c] * scale : -INFINITY;
+        const bool seen = (hi ? ok_hi : ok_lo) && key <= pos && pos - key < window && (chunk <= 0 || key >= pos - pos % chunk);
+        float v = s[j][c] * scale;
+        if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+        if (sig) v = seen ? 1.0f / (1.0f + __expf(-(v + sb))) : 0.f;  // the weight itself
+        else if (!seen) v = -INFINITY;
         s[j][c] = v;
         if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
       }
@@ -125,22 +138,33 @@ __global__ void __launch_bounds__(128)
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float mn_lo = sig ? 0.f : fmaxf(m_lo, mx_lo), mn_hi = sig ? 0.f : fmaxf(m_hi, mx_hi);
     // a row that has seen no key yet (no sink, every key of the tile masked) keeps m = -inf: nothing to rescale
     const float c_lo = mn_lo == -INFINITY ? 1.0f : __expf(m_lo - mn_lo), c_hi = mn_hi == -INFINITY ? 1.0f : __expf(m_hi - mn_hi);
     m_lo = mn_lo;
     m_hi = mn_hi;
     l_lo *= c_lo;
     l_hi *= c_hi;
-    uint32_t pf[4][2];  // P as bf16 pairs: [n8 tile][row half]
+    uint32_t pf[4][2], pr[4][2];  // P as bf16 pairs: [n8 tile][row half]; pr = what bf16 rounding left over (split_p)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float p0 = mn_lo == -INFINITY ? 0.f : __expf(s[j][0] - mn_lo), p1 = mn_lo == -INFINITY ? 0.f : __expf(s[j][1] - mn_lo);
-      const float p2 = mn_hi == -INFINITY ? 0.f : __expf(s[j][2] - mn_hi), p3 = mn_hi == -INFINITY ? 0.f : __expf(s[j][3] - mn_hi);
+      float p0, p1, p2, p3;
+      if (sig) {
+        p0 = s[j][0], p1 = s[j][1], p2 = s[j][2], p3 = s[j][3];
+      } else {
+        p0 = mn_lo == -INFINITY ? 0.f : __expf(s[j][0] - mn_lo), p1 = mn_lo == -INFINITY ? 0.f : __expf(s[j][1] - mn_lo);
+        p2 = mn_hi == -INFINITY ? 0.f : __expf(s[j][2] - mn_hi), p3 = mn_hi == -INFINITY ? 0.f : __expf(s[j][3] - mn_hi);
+      }
       l_lo += p0 + p1;
       l_hi += p2 + p3;
       pf[j][0] = pack_bf16(p0, p1);
       pf[j][1] = pack_bf16(p2, p3);
+      if (split_p) {
+        const float2 h0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pf[j][0]));
+        const float2 h1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pf[j][1]));
+        pr[j][0] = pack_bf16(p0 - h0.x, p1 - h0.y);
+        pr[j][1] = pack_bf16(p2 - h1.x, p3 - h1.y);
+      }
     }
 #pragma unroll
     for (int j = 0; j < 2 * DV16M; ++j) {
@@ -153,6 +177,7 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
       const uint32_t af[4] = {pf[2 * ks][0], pf[2 * ks][1], pf[2 * ks + 1][0], pf[2 * ks + 1][1]};
+      const uint32_t ar[4] = {pr[2 * ks][0], pr[2 * ks][1], pr[2 * ks + 1][0], pr[2 * ks + 1][1]};
 #pragma unroll
       for (int jd = 0; jd < DV16M; ++jd) {
         if (jd * 16 < Dv) {
@@ -161,6 +186,10 @@ __global__ void __launch_bounds__(128)
           ldmatrix_x4_trans(bf, smem_u32(Vs + (16 * ks + (mi & 1) * 8 + (lane & 7)) * ldv + jd * 16 + (mi >> 1) * 8));
           mma_bf16_16816(o[2 * jd], af, bf[0], bf[1]);
           mma_bf16_16816(o[2 * jd + 1], af, bf[2], bf[3]);
+          if (split_p) {
+            mma_bf16_16816(o[2 * jd], ar, bf[0], bf[1]);
+            mma_bf16_16816(o[2 * jd + 1], ar, bf[2], bf[3]);
+          }
         }
       }
     }
@@ -172,17 +201,23 @@ __global__ void __launch_bounds__(128)
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-  const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+  const float inv_lo = sig ? 1.0f : 1.0f / l_lo, inv_hi = sig ? 1.0f : 1.0f / l_hi;
 #pragma unroll
   for (int j = 0; j < 2 * DV16M; ++j) {
     const int d = 8 * j + 2 * (lane & 3);
     if (d < Dv) {
-      if (ok_lo)
-        *reinterpret_cast<__nv_bfloat162*>(out + ((int64_t)(t0 + i0 + r_lo) * H + h) * Dv + d) =
-            __floats2bfloat162_rn(o[j][0] * inv_lo, o[j][1] * inv_lo);
-      if (ok_hi)
-        *reinterpret_cast<__nv_bfloat162*>(out + ((int64_t)(t0 + i0 + r_lo + 8) * H + h) * Dv + d) =
-            __floats2bfloat162_rn(o[j][2] * inv_hi, o[j][3] * inv_hi);
+      const int64_t a_lo = ((int64_t)(t0 + i0 + r_lo) * H + h) * Dv + d, a_hi = a_lo + (int64_t)8 * H * Dv;
+      if (out_f32) {
+        if (ok_lo) *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + a_lo) = make_float2(o[j][0] * inv_lo, o[j][1] * inv_lo);
+        if (ok_hi) *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + a_hi) = make_float2(o[j][2] * inv_hi, o[j][3] * inv_hi);
+      } else {
+        if (ok_lo)
+          *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(out) + a_lo) =
+              __floats2bfloat162_rn(o[j][0] * inv_lo, o[j][1] * inv_lo);
+        if (ok_hi)
+          *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(out) + a_hi) =
+              __floats2bfloat162_rn(o[j][2] * inv_hi, o[j][3] * inv_hi);
+      }
     }
   }
 }
@@ -196,10 +231,13 @@ extern "C" {
 int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
                                int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
-                               int Dv, int v_pitch, int block_size, void* stream) {
+                               int Dv, int v_pitch, int block_size, int chunk, float softcap, const float* sigmoid_bias, int v_div,
+                               int out_f32, int split_p, void* stream) {
   B200_REQUIRE(q && k_pool && v_pool && block_table && seq_start && seq_slot && seq_pos0 && out,
                "swa_sink_attn_prefill: null pointer");
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && window >= 1, "swa_sink_attn_prefill: %d query heads over %d kv heads", H, G);
+  B200_REQUIRE(chunk >= 0 && v_div >= 1 && G % v_div == 0 && (v_div == 1 || v_pool != k_pool) && !(sigmoid_bias && sink),
+               "swa_sink_attn_prefill: chunk %d, %d key heads sharing values by %d", chunk, G, v_div);
   if (D % 16 || Dv % 16 || Dv > 256 || D > 512 || v_pitch % 8 || v_pitch < Dv || (ldq & 1) || ((uintptr_t)q & 7)) {
     set_last_error("swa_sink_attn_prefill: head sizes %d / %d need multiples of 16 (<= 512 / 256)", D, Dv);
     return B200_ERR_UNSUPPORTED;
@@ -215,7 +253,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
       B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_prefill_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     B200_CUDA_OK(launch_kernel(swa_sink_prefill_kernel<M>, grid, dim3(128), smem, st, q, ldq, (const BT*)k_pool,              \
                                (const BT*)v_pool, block_table, bt_stride, seq_start, seq_slot, seq_pos0, sink, scale, window, \
-                               (BT*)out, H, G, D, Dv, block_size, v_pitch));                                                           \
+                               out, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p));         \
   } while (0)
   if (Dv <= 64) PF_LAUNCH(4);
   else if (Dv <= 128) PF_LAUNCH(8);

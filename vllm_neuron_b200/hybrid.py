@@ -31,6 +31,21 @@ head . Rf(x) * logit_scale.  Mixers:
 Feed-forward: dense W_down(gelu_tanh(W_gate h) * W_up h), or SiLU experts chosen by the `top` largest router logits (+ bias)
 and weighed, on their OUTPUTS, by the softmax over the chosen logits.
 
+A third block style, parallel branches behind one grouped RMS norm (the "Zudarax" design):
+  h = N(x);  x += mixer(h) + ff(h)   with N cutting a row into `norm.groups` equal parts, each divided by its own RMS, times w.
+Mixers are rotating attentions over the paged pools, all one code path with per-layer variants (`RotAttnSpec`):
+  * 'attention'   -- biased q / k / v projections, a short causal convolution on each (no activation), an RMS norm over the whole
+                     q and k projection, rotary positions on the leading rot.dims columns of a head (pairs (i, i + dims/2)),
+                     soft-capped scores, keys confined to the query's chunk of mask.size positions, softmax;
+  * 'attention_2' -- differential attention: two score maps per head over the same values, a1 - lambda a2 with
+                     lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, a weightless per-head RMS norm times (1 - diff), and a
+                     per-head sigmoid output gate read from the mixer's input;
+  * 'attention_3' -- short convolutions, YaRN-blended rotary frequencies, causal, weights sigmoid(score + bias[head]) that are
+                     not normalised over the keys.
+Feed-forward: W_down P(W_up h) with the polynomial activation P(z) = a N(z) + b N(z^2) + c N(z^3) + e, N = division by the
+row's RMS.  q / k / v (/ gate) and W_up are ONE GEMM, since both branches read the same h.  State per sequence: the K / V pages
+and the last taps - 1 projected (biased) inputs of the convolutions.
+
 The step is ONE ragged batch (`StepMeta`): portions of prompts and single decoded tokens run through the same kernels, each
 sequence continuing from its KV pages (block table row) and its state slot.  fp32 everywhere the design asks for it
 (residual stream, norms, softmax, router, recurrence); GEMM operands, weights and KV pools are bf16, or fp32 when the model is
@@ -50,7 +65,8 @@ from . import ops
 
 ARCHITECTURE = "Pumopel"
 # block style per architecture: how the norms sit around the sublayers (and which norm it is)
-BLOCK_STYLES = {"Pumopel": "dyt_sandwich", "Kenetar": "rms_post"}
+BLOCK_STYLES = {"Pumopel": "dyt_sandwich", "Kenetar": "rms_post", "Zudarax": "rms_parallel"}
+ROT_ATTN_KINDS = ("attention", "attention_2", "attention_3")  # the parallel style's mixers
 _NO_WINDOW = 1 << 30
 
 
@@ -107,10 +123,12 @@ class DeltaSpec:
 
 @dataclass
 class RotSpec:
-    """Rotary angles of interleaved pairs over the first `dims` columns; `scaling` (YaRN): factor, original, fast, slow."""
+    """Rotary angles over the first `dims` columns, pairs (2i, 2i + 1) or, with `half`, (i, i + dims / 2); `scaling` (YaRN):
+    factor, original, fast, slow."""
     dims: int
     base: float
     scaling: dict | None = None
+    half: bool = False
 
     def tables(self, positions: int):
         """(cos, sin) fp32 [positions, dims / 2], computed in float64.  Pair i turns by p * f_i, f_i = base^(-2i/dims); with
@@ -141,6 +159,51 @@ class LatentAttnSpec:
     q_rank: int
     scale: float
     rot: RotSpec = None
+
+
+@dataclass
+class RotAttnSpec:
+    """Rotating attention over paged K / V with per-layer variants; a variant that is off costs nothing."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: RotSpec = None
+    conv: int = 0            # taps of the short causal convolution on q, k and v (0: none)
+    bias: bool = False       # q / k / v projection biases
+    qk_norm: bool = False    # RMS norm over the whole q and k projection, weights per column
+    chunk: int = 0           # > 0: keys visible only inside the query's chunk of this many positions
+    softcap: float = 0.0     # > 0: cap * tanh(score / cap)
+    sigmoid: bool = False    # weights sigmoid(score + bias[head]) instead of a softmax
+    diff: float | None = None  # differential attention: two maps per head, this is the constant of lambda and of (1 - diff)
+    gate: bool = False       # per-head sigmoid output gate from the mixer's input
+
+    @property
+    def maps(self) -> int:
+        return 1 if self.diff is None else 2
+
+    @property
+    def q_cols(self) -> int:
+        return self.heads * self.maps * self.dim
+
+    @property
+    def k_cols(self) -> int:
+        return self.kv_heads * self.maps * self.dim
+
+    @property
+    def v_cols(self) -> int:
+        return self.kv_heads * self.vdim
+
+    @property
+    def channels(self) -> int:  # what the convolutions see: [q | k | v]
+        return self.q_cols + self.k_cols + self.v_cols
+
+
+@dataclass
+class PolySpec:
+    """Dense feed-forward with the polynomial unit-RMS activation."""
+    ff: int
 
 
 @dataclass
@@ -178,6 +241,7 @@ class HybridConfig:
     name: str = ARCHITECTURE
     bigram: dict | None = None   # buckets, mul_prev, mul_cur
     logit_scale: float = 1.0
+    norm_groups: int = 1         # parallel style: equal parts of a row that are normed on their own
 
     @property
     def style(self) -> str:
@@ -190,9 +254,14 @@ class HybridConfig:
         if name not in BLOCK_STYLES:
             raise ValueError(f"unknown hybrid architecture {name!r}")
         post = BLOCK_STYLES[name] == "rms_post"
+        par = BLOCK_STYLES[name] == "rms_parallel"
         for L in d["layers"]:
             m = L["mixer"]
-            if L["type"] == "mamba2":
+            if par:
+                if L["type"] not in ROT_ATTN_KINDS:
+                    raise ValueError(f"layer type {L['type']!r} is not part of the {name} design")
+                mixer = _rot_attn_spec(L["type"], m)
+            elif L["type"] == "mamba2":
                 mixer = SsmSpec(int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["conv"]),
                                 int(m.get("norm_groups", 1)))
                 if mixer.heads % mixer.groups or mixer.inner % mixer.norm_groups:
@@ -216,13 +285,17 @@ class HybridConfig:
                     raise ValueError(f"latent attention: {mixer.rot.dims} rotating columns in a rotated part of {mixer.rot_dim}")
             else:
                 raise ValueError(f"unknown layer type {L['type']!r}")
-            if post != (L["type"] in ("delta", "latent_attention")):
+            if not par and post != (L["type"] in ("delta", "latent_attention")):
                 raise ValueError(f"layer type {L['type']!r} is not part of the {name} design")
             f = L.get("mlp")
             mlp = None
             if f:
                 kind = f.get("kind", "moe")
-                if kind == "dense" and post:
+                if par:
+                    if kind != "dense":
+                        raise ValueError(f"unknown feed-forward kind {kind!r}")
+                    mlp = PolySpec(int(f["ff"]))
+                elif kind == "dense" and post:
                     mlp = DenseSpec(int(f["ff"]))
                 elif kind == "moe" and post:
                     mlp = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]), route="softmax_out")
@@ -233,11 +306,14 @@ class HybridConfig:
                 else:
                     raise ValueError(f"unknown feed-forward kind {kind!r}")
             layers.append(LayerSpec(L["type"], mixer, mlp))
-        emb = d["embedding"]
+        emb = d.get("embedding") or {}
         big = emb.get("bigram")
-        return HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), float(emb["scale"]), layers, name,
+        groups = int(d["norm"].get("groups", 1))
+        if int(d["width"]) % groups:
+            raise ValueError(f"rows of {d['width']} do not split into {groups} equal norm groups")
+        return HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), float(emb.get("scale", 1.0)), layers, name,
                             {k: int(big[k]) for k in ("buckets", "mul_prev", "mul_cur")} if big else None,
-                            float(d.get("logit_scale", 1.0)))
+                            float(d.get("logit_scale", 1.0)), groups)
 
     @staticmethod
     def from_pretrained(path: str) -> "HybridConfig":
@@ -248,13 +324,29 @@ class HybridConfig:
         """The configuration in its file form (what from_dict reads)."""
         out = {"architecture": self.name, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.eps},
                "embedding": {"scale": self.embed_scale}, "layers": []}
+        if self.style == "rms_parallel":
+            out["norm"]["groups"] = self.norm_groups
+            del out["embedding"]
         if self.bigram:
             out["embedding"]["bigram"] = dict(self.bigram)
         if self.style == "rms_post":
             out["logit_scale"] = self.logit_scale
         for L in self.layers:
             m = L.mixer
-            if L.kind == "delta":
+            if isinstance(m, RotAttnSpec):
+                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
+                         "rot": {"dims": m.rot.dims, "base": m.rot.base}}
+                if m.rot.scaling:
+                    mixer["rot"]["scaling"] = dict(m.rot.scaling)
+                if m.conv:
+                    mixer["conv"] = m.conv
+                if m.chunk:
+                    mixer["mask"] = {"size": m.chunk}
+                if m.softcap:
+                    mixer["softcap"] = m.softcap
+                if m.diff is not None:
+                    mixer["diff"] = m.diff
+            elif L.kind == "delta":
                 mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "conv": m.conv}
             elif L.kind == "latent_attention":
                 mixer = {"heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim, "kv_rank": m.kv_rank,
@@ -269,7 +361,7 @@ class HybridConfig:
                 if m.window != _NO_WINDOW:
                     mixer["mask"] = {"size": m.window}
             f = None
-            if isinstance(L.mlp, DenseSpec):
+            if isinstance(L.mlp, (DenseSpec, PolySpec)):
                 f = {"kind": "dense", "ff": L.mlp.ff}
             elif L.mlp and L.mlp.route == "softmax_out":
                 f = {"kind": "moe", "router": {"experts": L.mlp.experts, "top": L.mlp.top}, "expert": {"ff": L.mlp.ff}}
@@ -281,6 +373,29 @@ class HybridConfig:
         return out
 
 
+def _rot_attn_spec(kind: str, m: dict) -> RotAttnSpec:
+    """One of the parallel style's mixers from its configuration entry.  The kind fixes which mechanisms a layer has; every
+    size and constant comes from the entry."""
+    r = m["rot"]
+    rot = RotSpec(int(r["dims"]), float(r["base"]), dict(r["scaling"]) if r.get("scaling") else None, half=True)
+    spec = RotAttnSpec(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), float(m["scale"]), rot)
+    if spec.heads % spec.kv_heads:
+        raise ValueError(f"{kind} layer: {spec.heads} query heads over {spec.kv_heads} kv heads")
+    if rot.dims % 2 or rot.dims > spec.dim:
+        raise ValueError(f"{kind} layer: {rot.dims} rotating columns in heads of {spec.dim}")
+    if kind == "attention":
+        spec.bias = spec.qk_norm = True
+        spec.conv = int(m.get("conv") or 0)
+        spec.chunk = int((m.get("mask") or {}).get("size") or 0)
+        spec.softcap = float(m.get("softcap") or 0.0)
+    elif kind == "attention_2":
+        spec.diff, spec.gate = float(m["diff"]), True
+    else:
+        spec.sigmoid = True
+        spec.conv = int(m.get("conv") or 0)
+    return spec
+
+
 def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
     """Checkpoint tensor name -> shape (a linear layer's matrix has one row per output)."""
     W = cfg.width
@@ -289,8 +404,10 @@ def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
     if cfg.bigram:
         s["bigram"] = (cfg.bigram["buckets"] + 1, W)
 
+    par = cfg.style == "rms_parallel"
+
     def norm(n):
-        if post:
+        if post or par:
             s[n] = (W,)
         else:
             s[n], s[n + ".b"], s[n + ".alpha"] = (W,), (W,), ()
@@ -298,10 +415,27 @@ def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
     norm("final.norm")
     for i, L in enumerate(cfg.layers):
         p = f"l{i}."
-        for n in (("norm1",) + (("norm2",) if L.mlp else ())) if post else (("norm1", "norm1b") + (("norm2", "norm2b") if L.mlp else ())):
+        for n in ("norm1",) if par else (("norm1",) + (("norm2",) if L.mlp else ())) if post else \
+                (("norm1", "norm1b") + (("norm2", "norm2b") if L.mlp else ())):
             norm(p + n)
         m = L.mixer
-        if L.kind == "delta":
+        if isinstance(m, RotAttnSpec):
+            s.update({p + "mix.q": (m.q_cols, W), p + "mix.k": (m.k_cols, W), p + "mix.v": (m.v_cols, W),
+                      p + "mix.o": (W, m.heads * m.vdim)})
+            for n, c in (("q", m.q_cols), ("k", m.k_cols), ("v", m.v_cols)):
+                if m.bias:
+                    s[f"{p}mix.{n}.b"] = (c,)
+                if m.conv:
+                    s[f"{p}mix.{n}.conv"] = (c, m.conv)
+                if m.qk_norm and n != "v":
+                    s[f"{p}mix.{n}.norm"] = (c,)
+            if m.sigmoid:
+                s[p + "mix.pb"] = (m.heads,)
+            if m.diff is not None:
+                s.update({p + "mix." + n: (m.dim,) for n in ("lq1", "lk1", "lq2", "lk2")})
+            if m.gate:
+                s[p + "mix.g"] = (m.heads, W)
+        elif L.kind == "delta":
             gd, hp = m.kv_heads * m.dim, m.heads * m.vdim
             s.update({p + "mix.q": (gd, W), p + "mix.q.conv": (gd, m.conv), p + "mix.k": (gd, W), p + "mix.k.conv": (gd, m.conv),
                       p + "mix.v": (hp, W), p + "mix.v.conv": (hp, m.conv), p + "mix.b": (m.heads, W), p + "mix.a": (m.heads, W),
@@ -322,7 +456,9 @@ def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
             if m.v_mix:
                 s[p + "mix.vmix"] = ()
         f = L.mlp
-        if isinstance(f, DenseSpec):
+        if isinstance(f, PolySpec):
+            s.update({p + "mlp.up": (f.ff, W), p + "mlp.down": (W, f.ff), p + "mlp.act": (4,)})
+        elif isinstance(f, DenseSpec):
             s.update({p + "mlp.gate": (f.ff, W), p + "mlp.up": (f.ff, W), p + "mlp.down": (W, f.ff)})
         elif f:
             s[p + "mlp.router"] = (f.experts, W)
@@ -351,6 +487,12 @@ def random_weights(cfg: HybridConfig, seed: int = 0, std: float | None = None) -
             t = 0.2 + 0.5 * torch.rand((), generator=g)
         elif leaf == "b" and len(shape) == 1:
             t = 0.05 * torch.randn(shape, generator=g)
+        elif leaf == "act":
+            t = torch.tensor([0.6, 0.3, 0.2, 0.05]) + 0.1 * torch.randn(shape, generator=g)
+        elif leaf == "pb":
+            t = -2.0 + torch.randn(shape, generator=g)
+        elif leaf in ("lq1", "lk1", "lq2", "lk2"):
+            t = 0.3 * torch.randn(shape, generator=g)
         elif leaf in ("norm1", "norm2", "norm1b", "norm2b", "norm") and len(shape) == 1:
             t = 1.0 + 0.1 * torch.randn(shape, generator=g)
         elif leaf == "A_log":
@@ -478,9 +620,10 @@ class HybridCausalLM:
             return get(name).to(dev, torch.float32).contiguous()
 
         post = cfg.style == "rms_post"
+        par = cfg.style == "rms_parallel"
 
         def norm(name):
-            if post:  # RMS norm, weight stored around zero
+            if post or par:  # RMS norm: weight stored around zero (post-norm) or plain, in groups (parallel)
                 return vec(name)
             return (vec(name), vec(name + ".b"), float(get(name + ".alpha").float()))
 
@@ -499,9 +642,37 @@ class HybridCausalLM:
         for i, L in enumerate(cfg.layers):
             p, m = f"l{i}.", L.mixer
             lw = {"spec": L, "norm1": norm(p + "norm1")}
-            if not post:
+            if not post and not par:
                 lw["norm1b"] = norm(p + "norm1b")
-            if L.kind == "delta":
+            if isinstance(m, RotAttnSpec):
+                key = (m.rot.dims, m.rot.base, json.dumps(m.rot.scaling, sort_keys=True))
+                if key not in rot_tables:
+                    rot_tables[key] = tuple(t.to(dev) for t in m.rot.tables(self.max_blocks * block_size))
+                wq = get(p + "mix.q")
+                if m.diff is not None:
+                    # two maps per head, stored head by head as [map 1 | map 2]: the query rows are re-laid per kv group as
+                    # [the group's first maps | its second maps], so that query head i reads key head i // (heads / kv_heads)
+                    # of the 2 * kv_heads key heads (kv head g's maps are key heads 2g and 2g + 1, both over value head g)
+                    rep = m.heads // m.kv_heads
+                    wq = wq.view(m.kv_heads, rep, 2, m.dim, -1).transpose(1, 2).reshape(m.q_cols, -1)
+                    f64 = lambda n: get(p + "mix." + n).double()
+                    lw["lam"] = float(torch.exp((f64("lq1") * f64("lk1")).sum()) - torch.exp((f64("lq2") * f64("lk2")).sum()) + m.diff)
+                names = [p + "mix.k", p + "mix.v"] + ([p + "mix.g"] if m.gate else []) + ([p + "mlp.up"] if L.mlp else [])
+                lw.update(w_in=torch.cat([wq] + [get(n) for n in names], dim=0).to(dev, et).contiguous(), w_o=lin(p + "mix.o"),
+                          rot=rot_tables[key],
+                          k_pool=torch.zeros((num_blocks, m.kv_heads * m.maps, block_size, m.dim), dtype=et, device=dev),
+                          v_pool=torch.zeros((num_blocks, m.kv_heads, block_size, m.vdim), dtype=et, device=dev))
+                if m.bias:
+                    lw["in_bias"] = torch.cat([get(p + f"mix.{n}.b") for n in "qkv"]).to(dev, torch.float32).contiguous()
+                if m.conv or m.bias:  # taps == 0 with a bias: one tap of weight 1 adds the bias
+                    cw = torch.cat([get(p + f"mix.{n}.conv") for n in "qkv"]) if m.conv else torch.ones((m.channels, 1))
+                    lw.update(conv_w=cw.to(dev, torch.float32).contiguous(),
+                              conv_state=torch.zeros((slots, max(cw.shape[1] - 1, 1), m.channels), dtype=torch.float32, device=dev))
+                if m.qk_norm:
+                    lw.update(q_norm=vec(p + "mix.q.norm"), k_norm=vec(p + "mix.k.norm"))
+                if m.sigmoid:
+                    lw["pb"] = vec(p + "mix.pb")
+            elif L.kind == "delta":
                 lw.update(w_in=lin(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.b", p + "mix.a", p + "mix.g"),
                           conv_w=torch.cat([get(p + "mix.q.conv"), get(p + "mix.k.conv"), get(p + "mix.v.conv")]
                                            ).to(dev, torch.float32).contiguous(),
@@ -540,11 +711,13 @@ class HybridCausalLM:
                         raise ValueError("value mixing needs the same kv_heads * vdim in every v_mix layer")
                     first_vmix = False
             f = L.mlp
-            if f:
+            if f and not par:
                 lw["norm2"] = norm(p + "norm2")
                 if not post:
                     lw["norm2b"] = norm(p + "norm2b")
-            if isinstance(f, DenseSpec):
+            if isinstance(f, PolySpec):  # W_up rides in w_in
+                lw.update(w_down=lin(p + "mlp.down"), act=vec(p + "mlp.act"))
+            elif isinstance(f, DenseSpec):
                 lw.update(w_gu=lin(p + "mlp.gate", p + "mlp.up"), w_down=lin(p + "mlp.down"))
             elif f:
                 lw["w_router"] = lin(p + "mlp.router")
@@ -566,15 +739,16 @@ class HybridCausalLM:
     # ------------------------------------------------------------------ sizes
     def kv_bytes_per_block(self) -> int:
         es = 2 if self.et == torch.bfloat16 else 4
-        return sum(L.mixer.kv_heads * self.block_size * (L.mixer.dim + L.mixer.vdim) * es
-                   for L in self.cfg.layers if L.kind == "attention") + \
+        return sum(L.mixer.kv_heads * self.block_size * (L.mixer.dim * getattr(L.mixer, "maps", 1) + L.mixer.vdim) * es
+                   for L in self.cfg.layers if isinstance(L.mixer, (AttnSpec, RotAttnSpec))) + \
             sum(self.block_size * (L.mixer.kv_rank + L.mixer.rot_dim) * es for L in self.cfg.layers if L.kind == "latent_attention")
 
     def state_bytes_per_slot(self) -> int:
         return sum(4 * (L.mixer.heads * L.mixer.state * L.mixer.vdim + (L.mixer.conv - 1) * L.mixer.channels)
                    for L in self.cfg.layers if L.kind == "mamba2") + \
             sum(4 * (L.mixer.heads * L.mixer.dim * L.mixer.vdim + (L.mixer.conv - 1) * L.mixer.channels)
-                for L in self.cfg.layers if L.kind == "delta") + (4 if self.cfg.bigram else 0)
+                for L in self.cfg.layers if L.kind == "delta") + (4 if self.cfg.bigram else 0) + \
+            sum(4 * max(L.mixer.conv - 1, 0) * L.mixer.channels for L in self.cfg.layers if isinstance(L.mixer, RotAttnSpec))
 
     # ------------------------------------------------------------------ building blocks
     def _linear(self, a, w):
@@ -639,6 +813,48 @@ class HybridCausalLM:
                            gate=proj[:, m.q_rank + kr:])
         return self._linear(vals, lw["w_o"])
 
+    def _rot_attention(self, lw, proj, meta):
+        """A rotating attention of the parallel style from the joint projection rows proj = fp32 [T, q | k | v | (gate) | (up)]."""
+        m = lw["spec"].mixer
+        src = proj
+        if "conv_w" in lw:  # short convolutions over [q | k | v] (the projection's bias joins its inputs), no activation
+            src = ops.causal_conv_silu(proj, 0, m.channels, lw["conv_w"], None, lw["conv_state"], meta, torch.float32,
+                                       in_bias=lw.get("in_bias"), silu=False)
+        cos, sin = lw["rot"]
+        hq = m.heads * m.maps
+        q = ops.qk_norm_rope_kv_write(src, 0, m.q_cols, m.q_cols + m.k_cols, hq, lw["k_pool"], lw["v_pool"], meta,
+                                      q_norm=lw.get("q_norm"), k_norm=lw.get("k_norm"), eps=self.cfg.eps, rot_n=m.rot.dims,
+                                      rot_half=m.rot.half, cos=cos, sin=sin)
+        a = ops.swa_sink_attn(q, hq, lw["k_pool"], lw["v_pool"], self.block_table, meta, None, m.scale, _NO_WINDOW, chunk=m.chunk,
+                              softcap=m.softcap, sigmoid_bias=lw.get("pb"), out_f32=m.diff is not None, split_p=True)
+        if m.diff is not None:  # both maps' outputs stay fp32 until they are combined and normed
+            a = ops.diff_head_norm_gate(a, lw["lam"], 1.0 - m.diff, proj if m.gate else None, m.channels, self.cfg.eps, m.heads,
+                                        m.heads // m.kv_heads, self.et)
+        return self._linear(a, lw["w_o"])
+
+    def _forward_parallel(self, tokens, meta, logit_rows, capture):
+        """h = N(x); x += mixer(h) + ff(h): one grouped norm per layer, one GEMM for everything that reads h, and one pass over
+        the residual per layer that adds both branches and norms for the next layer (or for the logits)."""
+        et, cfg, n = self.et, self.cfg, len(self.layers)
+        x = ops.embed_scale(tokens, self.embed, cfg.embed_scale)
+        h = ops.add_group_rmsnorm(x, None, None, self.layers[0]["norm1"] if n else self.final_norm, cfg.norm_groups, cfg.eps, et)
+        for i, lw in enumerate(self.layers):
+            m, f = lw["spec"].mixer, lw["spec"].mlp
+            proj = self._linear(h, lw["w_in"])
+            y = self._rot_attention(lw, proj, meta)
+            y2 = None
+            if f:
+                y2 = self._linear(ops.poly_norm(proj, m.channels + (m.heads if m.gate else 0), f.ff, lw["act"], cfg.eps, et), lw["w_down"])
+            h = ops.add_group_rmsnorm(x, y, y2, self.layers[i + 1]["norm1"] if i + 1 < n else self.final_norm, cfg.norm_groups,
+                                      cfg.eps, et)
+            if capture is not None:
+                capture.append(x.clone())
+        if logit_rows is None or logit_rows.numel() == 0:
+            self.last_logits = None
+            return None
+        self.last_logits = self._linear(h.index_select(0, logit_rows).contiguous(), self.head)
+        return self.last_logits
+
     def _post_ff(self, lw, h):
         """Feed-forward of the post-norm style -> (fp32 branch rows, rows per token, their weights or None)."""
         f = lw["spec"].mlp
@@ -688,6 +904,8 @@ class HybridCausalLM:
         capture: a list that is given, layer by layer, a copy of x as that layer leaves it."""
         if self.cfg.style == "rms_post":
             return self._forward_post(tokens, meta, logit_rows, capture)
+        if self.cfg.style == "rms_parallel":
+            return self._forward_parallel(tokens, meta, logit_rows, capture)
         et, n = self.et, len(self.layers)
         x = ops.embed_scale(tokens, self.embed, self.cfg.embed_scale)
         h = ops.dyt_norm(x, *self.layers[0]["norm1"], et) if n else None

@@ -671,19 +671,21 @@ def clamped_glu(gate_up, limit: float, out_dtype):
     return out
 
 
-def causal_conv_silu(src, col0: int, channels: int, conv_w, conv_b, state, meta, out_dtype):
+def causal_conv_silu(src, col0: int, channels: int, conv_w, conv_b, state, meta, out_dtype, *, in_bias=None, silu: bool = True):
     """Columns [col0, col0 + channels) of the fp32 rows `src` -> SiLU(conv) [T, channels]; `state` [slots, taps-1, channels]
-    fp32 is read for continuing sequences and updated for all."""
-    _cuda(src, conv_w, conv_b, state)  # conv_b may be None (no bias)
-    _f32(src, conv_w, conv_b, state)
+    fp32 is read for continuing sequences and updated for all.  in_bias fp32 [channels]: added to the inputs read from `src`
+    (a projection's bias; the state holds biased inputs).  silu False: the convolution alone."""
+    _cuda(src, conv_w, conv_b, state, in_bias)  # conv_b may be None (no bias)
+    _f32(src, conv_w, conv_b, state, in_bias)
     t, taps = src.shape[0], conv_w.shape[1]
     assert conv_w.shape[0] == channels and state.shape[1:] == (max(taps - 1, 1), channels)  # one unused row when taps == 1
     out = torch.empty((t, channels), dtype=out_dtype, device=src.device)
-    with _k("causal_conv_silu"):
-        check(_cabi.load().b200_causal_conv_silu(_ptr(src), src.stride(0), col0, _ptr(conv_w), _ptr(conv_b), _ptr(state),
-                                                 _ptr(meta.tok_seq), _ptr(meta.seq_start), _ptr(meta.seq_slot), _ptr(meta.seq_pos0),
-                                                 _ptr(out), _edt(out), t, meta.num_seqs, channels, taps, _stream()),
-              "b200_causal_conv_silu")
+    assert in_bias is None or in_bias.numel() == channels
+    with _k("causal_conv_silu" if silu else "causal_conv"):
+        check(_cabi.load().b200_causal_conv(_ptr(src), src.stride(0), col0, _ptr(conv_w), _ptr(conv_b), _ptr(in_bias), 1 if silu else 0,
+                                            _ptr(state), _ptr(meta.tok_seq), _ptr(meta.seq_start), _ptr(meta.seq_slot),
+                                            _ptr(meta.seq_pos0), _ptr(out), _edt(out), t, meta.num_seqs, channels, taps, _stream()),
+              "b200_causal_conv")
     return out
 
 
@@ -731,12 +733,17 @@ PREFILL_ATTN_MIN_TOKENS = 16  # longest portion of a step from which the tensor-
 
 
 def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink, scale: float, window: int,
-                  latent_values: int = 0):
+                  latent_values: int = 0, *, chunk: int = 0, softcap: float = 0.0, sigmoid_bias=None, out_f32: bool = False,
+                  split_p: bool = False):
     """q = the first num_heads * D columns of the fp32 rows q_src -> [T, num_heads * Dv] in the pools' element type.
     sink None: ordinary softmax.  latent_values = C > 0: v_pool is ignored and the values are the first C columns of the key
-    rows (attention over cached latents: one pool holds both)."""
-    _cuda(q_src, k_pool, v_pool, block_table, sink)
-    _f32(q_src, sink)
+    rows (attention over cached latents: one pool holds both).
+    chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0).  softcap > 0:
+    scaled scores pass through softcap * tanh(s / softcap).  sigmoid_bias fp32 [H]: weights sigmoid(s + bias[h]), not normalised
+    over keys.  A value pool with fewer heads than the key pool: consecutive key heads share a value head (two score maps over
+    the same values).  out_f32: fp32 rows.  split_p: the tensor-core kernel carries the weights as two bf16 terms."""
+    _cuda(q_src, k_pool, v_pool, block_table, sink, sigmoid_bias)
+    _f32(q_src, sink, sigmoid_bias)
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     _, g, bs, d = k_pool.shape
     if latent_values:
@@ -744,8 +751,12 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
         assert g == 1 and dv <= d
     else:
         dv = v_pitch = v_pool.shape[3]
+    v_div = g // v_pool.shape[1]
+    assert v_pool.shape[1] * v_div == g and v_pool.shape[2] == bs
     t = q_src.shape[0]
-    out = torch.empty((t, num_heads * dv), dtype=k_pool.dtype, device=q_src.device)
+    out = torch.empty((t, num_heads * dv), dtype=torch.float32 if out_f32 else k_pool.dtype, device=q_src.device)
+    variant = (int(chunk), float(softcap), _ptr(sigmoid_bias), v_div, 1 if out_f32 else 0)
+    plain = not chunk and not softcap and sigmoid_bias is None and v_div == 1 and not out_f32
     # prompt portions in bf16 serving: the tensor-core kernel; decode-sized steps, fp32 pools and odd head sizes: one CTA per
     # (token, head) on the CUDA cores
     if (k_pool.dtype == torch.bfloat16 and meta.max_new >= PREFILL_ATTN_MIN_TOKENS and d % 16 == 0 and dv % 16 == 0
@@ -754,10 +765,11 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
             check(_cabi.load().b200_swa_sink_attn_prefill(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                                           block_table.stride(0), _ptr(meta.seq_start), _ptr(meta.seq_slot),
                                                           _ptr(meta.seq_pos0), meta.num_seqs, meta.max_new, _ptr(sink), float(scale),
-                                                          int(window), _ptr(out), num_heads, g, d, dv, v_pitch, bs, _stream()),
+                                                          int(window), _ptr(out), num_heads, g, d, dv, v_pitch, bs, *variant,
+                                                          1 if split_p else 0, _stream()),
                   "b200_swa_sink_attn_prefill")
         return out
-    if (latent_values and sink is None and window >= (1 << 30) and k_pool.dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0
+    if (plain and latent_values and sink is None and window >= (1 << 30) and k_pool.dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0
             and dv <= 256 and q_src.stride(0) % 2 == 0):
         # attention over cached latents, decode-sized steps: the heads of a token are the rows of a tensor-core tile
         with _k("latent_attn_decode"):
@@ -769,7 +781,7 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
         check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
                                               _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
                                               _ptr(sink), float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, v_pitch, bs,
-                                              _stream()), "b200_swa_sink_attn")
+                                              *variant, _stream()), "b200_swa_sink_attn")
     return out
 
 
@@ -1005,3 +1017,74 @@ def latent_q_prep(q, heads: int, dim: int, rot_dim: int, rot_n: int, kv_rank: in
                                               _ptr(meta.tok_pos), _ptr(nope), _edt(nope), _ptr(q_att), t, _stream()),
               "b200_latent_q_prep")
     return nope, q_att
+
+
+# ------------------------------------------------------------------ parallel-branch decoders (grouped norm, rotating attention variants)
+def add_group_rmsnorm(x, y1, y2, w, groups: int, eps: float, out_dtype=None):
+    """x += y1 + y2 (fp32 rows, any pitch; y2 or both may be None), in place; returns the grouped RMS norm of x times w in
+    out_dtype (each of the `groups` equal consecutive parts of a row divided by its own RMS), or None when out_dtype is None."""
+    _cuda(x, y1, y2, w)
+    _f32(x, w)
+    t, width = x.shape
+    for y in (y1, y2):
+        assert y is None or (y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (t, width))
+    out = torch.empty((t, width), dtype=out_dtype, device=x.device) if out_dtype is not None else None
+    with _k("add_group_rmsnorm"):
+        check(_cabi.load().b200_add_group_rmsnorm(_ptr(x), _ptr(y1), y1.stride(0) if y1 is not None else 0, _ptr(y2),
+                                                  y2.stride(0) if y2 is not None else 0, _ptr(w), int(groups), float(eps), _ptr(out),
+                                                  _edt(out) if out is not None else F32, t, width, _stream()), "b200_add_group_rmsnorm")
+    return out
+
+
+def poly_norm(src, col0: int, n: int, coef, eps: float, out_dtype):
+    """Columns [col0, col0 + n) of the fp32 rows src -> a N(z) + b N(z^2) + c N(z^3) + e [T, n] in out_dtype; coef fp32 [4] =
+    (a, b, c, e); N divides a row by its RMS."""
+    _cuda(src, coef)
+    _f32(coef)
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and coef.numel() == 4
+    t = src.shape[0]
+    out = torch.empty((t, n), dtype=out_dtype, device=src.device)
+    with _k("poly_norm"):
+        check(_cabi.load().b200_poly_norm(_ptr(src), src.stride(0), col0, n, _ptr(coef), float(eps), _ptr(out), _edt(out), n, t,
+                                          _stream()), "b200_poly_norm")
+    return out
+
+
+def diff_head_norm_gate(a, lam: float, post: float, gate_src, gate_col0: int, eps: float, heads: int, rep: int, out_dtype):
+    """a fp32 [T, 2 * heads * P] (per kv group of `rep` heads: the first maps' rows, then the second maps') ->
+    [T, heads * P] = unit-RMS(a1 - lam * a2) * post * sigmoid(gate), gate = columns gate_col0.. of the fp32 rows gate_src
+    (None: no gate)."""
+    _cuda(a, gate_src)
+    _f32(a)
+    assert gate_src is None or (gate_src.dtype == torch.float32 and gate_src.stride(1) == 1)
+    t = a.shape[0]
+    p = a.shape[1] // (2 * heads)
+    out = torch.empty((t, heads * p), dtype=out_dtype, device=a.device)
+    with _k("diff_head_norm_gate"):
+        check(_cabi.load().b200_diff_head_norm_gate(_ptr(a), float(lam), float(post), _ptr(gate_src),
+                                                    gate_src.stride(0) if gate_src is not None else 0, gate_col0, float(eps),
+                                                    _ptr(out), _edt(out), t, heads, rep, p, _stream()), "b200_diff_head_norm_gate")
+    return out
+
+
+def qk_norm_rope_kv_write(src, q_col0: int, k_col0: int, v_col0: int, heads: int, k_pool, v_pool, meta, *, q_norm=None,
+                          k_norm=None, eps: float = 0.0, rot_n: int = 0, rot_half: bool = True, cos=None, sin=None):
+    """fp32 rows src = [.. q: heads * D .. k: G * D .. v: Gv * Dv ..] -> q fp32 [T, heads * D] (normed over the whole projection
+    when q_norm is given, leading rot_n columns of every head rotated by the token's position), and the step's keys (same
+    treatment) and values written into the pools [num_blocks, G, block_size, D] / [num_blocks, Gv, block_size, Dv]."""
+    _cuda(src, k_pool, v_pool, q_norm, k_norm, cos, sin)
+    _f32(q_norm, k_norm, cos, sin)
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and k_pool.dtype == v_pool.dtype
+    assert k_pool.is_contiguous() and v_pool.is_contiguous()
+    _, g, bs, d = k_pool.shape
+    _, gv, _, dv = v_pool.shape
+    assert rot_n == 0 or (cos.shape[1] == rot_n // 2 and sin.shape == cos.shape)
+    t = src.shape[0]
+    q = torch.empty((t, heads * d), dtype=torch.float32, device=src.device)
+    with _k("qk_norm_rope_kv_write"):
+        check(_cabi.load().b200_qk_norm_rope_kv_write(_ptr(src), src.stride(0), q_col0, k_col0, v_col0, _ptr(q_norm), _ptr(k_norm),
+                                                      float(eps), int(rot_n), 1 if rot_half else 0, _ptr(cos), _ptr(sin),
+                                                      _ptr(meta.tok_pos), _ptr(meta.slot_mapping), _ptr(q), _ptr(k_pool),
+                                                      _ptr(v_pool), _edt(k_pool), t, heads, g, gv, d, dv, bs, _stream()),
+              "b200_qk_norm_rope_kv_write")
+    return q

@@ -6,7 +6,8 @@ Two families are served:
     or a batch of decodes;
   * hybrid decoders (`HybridCausalLM`): config.json lists the layers; a step is one ragged batch.  "Pumopel": state-space /
     windowed-attention mixers, Dynamic-Tanh norms, MoE; "Kenetar": delta-rule / latent-attention mixers, post-norm RMS,
-    bigram embedding, dense or MoE feed-forward.
+    bigram embedding, dense or MoE feed-forward; "Zudarax": parallel mixer / feed-forward branches behind one grouped RMS
+    norm, three rotating-attention variants (chunked + soft-capped, differential, sigmoid), polynomial activation.
 The reference resolves the architecture the same way -- `hf_config.architectures[0]` picks the NxDI model class
 (vllm_neuron/worker/neuronx_distributed_model_loader.py:612-660).
 """
@@ -74,6 +75,7 @@ MODEL_REGISTRY: dict[str, ModelEntry] = {
     "Qwen2ForCausalLM": _DENSE,
     "Pumopel": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
     "Kenetar": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
+    "Zudarax": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
 }
 
 
