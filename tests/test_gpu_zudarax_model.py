@@ -1,0 +1,313 @@
+"""GPU: the parallel-branch decoder (Zudarax) through the stand-alone engine (runner step, page pool, state slots) against
+the plain restatement on whole sequences: whole prompts, token-by-token decoding from the first token, ragged portions down
+to two tokens, mixed batches with rows and pages that are freed and reused, decoding far past every chunk, configurations
+drawn at random, greedy generation through the scheduler and the trace command line.  The 32-bit mode is held to 1e-4 of
+the logit spread; the bf16 mode to its rounding noise."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer(kind, mlp, **mixer):
+    return {"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": mlp} if mlp else None}
+
+
+def _rot(dims, base, scaling=None):
+    r = {"dims": dims, "base": base}
+    if scaling:
+        r["scaling"] = scaling
+    return r
+
+
+def cfg_a():
+    """Sigmoid attention first; three norm groups; head sizes that are no multiple of 16 (the warp kernels in both modes) and
+    GEMM widths off the tensor cores; one kv head, and as many kv heads as heads; two and five taps; a chunk of 20 positions
+    (no multiple of the page); rotation over a whole head and over part of one; a layer without feed-forward; a cap of 4."""
+    yarn = {"factor": 5.0, "original": 40, "fast": 10.0, "slow": 2.0}
+    return {"architecture": "Zudarax", "vocab": 90, "width": 42, "norm": {"eps": 1e-5, "groups": 3}, "layers": [
+        _layer("attention_3", 50, heads=3, kv_heads=1, dim=12, vdim=20, conv=2, scale=0.29, rot=_rot(12, 700.0, yarn)),
+        _layer("attention_2", None, heads=4, kv_heads=4, dim=10, vdim=6, diff=0.3, scale=0.32, rot=_rot(4, 50.0)),
+        _layer("attention", 36, heads=2, kv_heads=2, dim=24, vdim=12, conv=5, scale=0.2, softcap=4.0, mask={"size": 20},
+               rot=_rot(10, 300.0)),
+        _layer("attention_2", 28, heads=6, kv_heads=2, dim=8, vdim=14, diff=0.8, scale=0.35, rot=_rot(8, 10000.0)),
+    ]}
+
+
+def cfg_b():
+    """Chunked attention first; one norm group; every GEMM on the tensor-core path and head sizes that put prompt portions of
+    16 tokens or more on the tensor-core attention kernel; one tap; a chunk of one page and a half."""
+    yarn = {"factor": 2.0, "original": 32, "fast": 8.0, "slow": 1.0}
+    return {"architecture": "Zudarax", "vocab": 200, "width": 64, "norm": {"eps": 1e-6, "groups": 1}, "layers": [
+        _layer("attention", 96, heads=4, kv_heads=1, dim=32, vdim=16, conv=1, scale=0.18, softcap=9.0, mask={"size": 48},
+               rot=_rot(32, 5000.0)),
+        _layer("attention_2", 80, heads=4, kv_heads=2, dim=16, vdim=32, diff=0.5, scale=0.25, rot=_rot(16, 1000.0)),
+        _layer("attention_3", None, heads=2, kv_heads=2, dim=48, vdim=48, conv=3, scale=0.14, rot=_rot(16, 100000.0, yarn)),
+        _layer("attention_3", 64, heads=8, kv_heads=2, dim=16, vdim=16, conv=2, scale=0.25, rot=_rot(8, 100.0)),
+    ]}
+
+
+class Case:
+    def __init__(self, cfgd, dtype, seed=0, max_num_seqs=3, pool_tokens=1024):
+        from vllm_neuron_b200.engine import B200Engine
+        from vllm_neuron_b200.hybrid import HybridConfig, random_weights
+
+        self.cfgd, self.dtype = cfgd, dtype
+        self.cfg = HybridConfig.from_dict(cfgd)
+        self.W = random_weights(self.cfg, seed=seed)
+        self.engine = B200Engine(self.cfg, self.W, dtype=dtype, max_num_seqs=max_num_seqs, max_pool_tokens=pool_tokens,
+                                 max_num_batched_tokens=1 << 20)
+        self.tol = 1e-4 if dtype == "float32" else 0.06
+        self._ref = {}
+
+    def tokens(self, n, seed):
+        return torch.randint(0, self.cfg.vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+    def ref(self, toks):
+        from oracle import zudarax_ref
+
+        key = tuple(toks)
+        if key not in self._ref:
+            self._ref[key] = zudarax_ref.forward(self.cfgd, self.W, toks)
+        return self._ref[key]
+
+    def replay(self, reqs, schedule):
+        """reqs: id -> tokens; schedule: list of steps, each [(id, n)].  Logits of every position, per request."""
+        at = {i: 0 for i in reqs}
+        got = {i: [] for i in reqs}
+        for step in schedule:
+            entries, end = [], []
+            for i, n in step:
+                entries.append((i, reqs[i][at[i]:at[i] + n], list(range(n))))
+                at[i] += n
+                if at[i] == len(reqs[i]):
+                    end.append(i)
+            taps = self.engine.replay_step(entries, end)
+            for i, n in step:
+                assert taps[i].shape == (n, self.cfg.vocab)
+                got[i].append(taps[i])
+        assert all(at[i] == len(reqs[i]) for i in reqs)
+        return {i: torch.cat(v) for i, v in got.items()}
+
+    def errs(self, got, toks):
+        want = self.ref(toks)
+        d = got.double() - want
+        d = d - d.mean(-1, keepdim=True)
+        spread = (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt()
+        return d.pow(2).mean(-1).sqrt() / spread
+
+    def check(self, got, reqs):
+        e = torch.cat([self.errs(got[i], toks) for i, toks in reqs.items()])
+        assert e.max().item() < self.tol, (e.max().item(), e.median().item())
+
+
+def _portions(n, sizes):
+    out, k = [], 0
+    while n > 0:
+        c = min(sizes[k % len(sizes)], n)
+        out.append(c)
+        n -= c
+        k += 1
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cfg", [cfg_a, cfg_b])
+def test_whole_prompt_decode_and_portions_agree_with_the_restatement(cfg, dtype):
+    c = Case(cfg(), dtype)
+    toks = c.tokens(150, 1)
+    whole = c.replay({"w": toks}, [[("w", 150)]])
+    c.check(whole, {"w": toks})
+    short = c.tokens(70, 2)
+    one_by_one = c.replay({"d": short}, [[("d", 1)] for _ in short])          # the first tokens, then decoding across chunk borders
+    c.check(one_by_one, {"d": short})
+    sizes = _portions(150, [2, 3, 2, 27, 30, 2, 1, 33, 7, 31, 1, 1, 10])     # cuts inside pages and chunks, and at their edges
+    cut = c.replay({"p": toks}, [[("p", n)] for n in sizes])
+    c.check(cut, {"p": toks})
+    d = (cut["p"] - whole["w"]).abs().max().item() / whole["w"].abs().max().item()
+    assert d < (1e-5 if dtype == "float32" else 0.05), d                      # how the prompt was cut does not matter
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_with_reused_rows_and_pages(dtype):
+    """Seven requests of unequal length (1 .. 130 tokens) through THREE rows and a pool that cannot hold them all at once:
+    portions beside single tokens, requests that sit out steps, rows, pages and convolution state taken over by later
+    requests."""
+    c = Case(cfg_a(), dtype, max_num_seqs=3, pool_tokens=320)
+    lens = {"a": 130, "b": 1, "c": 37, "d": 2, "e": 64, "f": 33, "g": 90}
+    reqs = {i: c.tokens(n, 10 + k) for k, (i, n) in enumerate(lens.items())}
+    sched = [
+        [("a", 40), ("b", 1), ("c", 2)],            # b ends: its row and page go back
+        [("a", 1), ("c", 30), ("d", 1)],
+        [("c", 1), ("d", 1)],                        # a sits out; d ends
+        [("a", 25), ("c", 1), ("e", 31)],
+        [("a", 1), ("c", 1), ("e", 1)],
+        [("a", 1), ("c", 2), ("e", 32)],            # c and e end
+        [("a", 62), ("f", 33), ("g", 2)],           # f is whole in one step and ends
+        [("g", 60)],
+        [("g", 1)], [("g", 1)],
+        [("g", 26)],
+    ]
+    got = c.replay(reqs, sched)
+    c.check(got, reqs)
+    assert c.engine.pool.num_free == c.engine.num_blocks - 1 and not c.engine.scheduler.running
+    if dtype == "float32":                                                     # each alone gives the same numbers
+        alone = Case(cfg_a(), dtype, max_num_seqs=1, pool_tokens=160)
+        for i in ("a", "e", "g"):
+            solo = alone.replay({i: reqs[i]}, [[(i, len(reqs[i]))]])
+            d = (solo[i] - got[i]).abs().max().item() / solo[i].abs().max().item()
+            assert d < 1e-5, (i, d)
+
+
+def _random_cfg(rng):
+    """A configuration drawn at random: 2-6 layers in any order, head counts, sizes, taps, chunk sizes, caps and norm groups
+    that need not be multiples of anything, with or without feed-forward and YaRN."""
+    width = rng.choice([48, 96, 120, 192, 240])
+    groups = rng.choice([g for g in (1, 2, 3, 4, 6, 8) if width % g == 0])
+    layers = []
+    for _ in range(rng.randint(2, 6)):
+        h = rng.choice([1, 2, 3, 4, 6, 8])
+        g = rng.choice([x for x in (1, 2, 3, 4, 6, 8) if h % x == 0])
+        d, v = rng.choice([8, 12, 16, 32, 40, 64]), rng.choice([8, 16, 20, 48, 80])
+        rot = _rot(rng.choice([x for x in (2, 4, 8, 12, 16, 32, 64) if x <= d]), rng.choice([100.0, 10000.0, 500000.0]))
+        mlp = None if rng.random() < 0.2 else rng.choice([24, 64, 100])
+        scale = rng.choice([d ** -0.5, 0.1, 0.3])
+        kind = rng.choice(["attention", "attention_2", "attention_3"])
+        if kind == "attention":
+            layers.append(_layer(kind, mlp, heads=h, kv_heads=g, dim=d, vdim=v, conv=rng.choice([1, 2, 3, 4, 7]), scale=scale,
+                                 softcap=rng.choice([2.0, 15.0, 50.0]), mask={"size": rng.choice([1, 5, 32, 100, 4096])}, rot=rot))
+        elif kind == "attention_2":
+            layers.append(_layer(kind, mlp, heads=h, kv_heads=g, dim=d, vdim=v, diff=rng.choice([0.1, 0.5, 0.9]), scale=scale, rot=rot))
+        else:
+            if rng.random() < 0.7:
+                rot["scaling"] = {"factor": rng.choice([2.0, 4.0, 40.0]), "original": rng.choice([16, 64, 4096]),
+                                  "fast": rng.choice([8.0, 32.0]), "slow": rng.choice([1.0, 2.0])}
+            layers.append(_layer(kind, mlp, heads=h, kv_heads=g, dim=d, vdim=v, conv=rng.choice([1, 2, 4, 6]), scale=scale, rot=rot))
+    return {"architecture": "Zudarax", "vocab": rng.choice([100, 257, 512]), "width": width,
+            "norm": {"eps": rng.choice([1e-6, 1e-5]), "groups": groups}, "layers": layers}
+
+
+@pytest.mark.parametrize("seed", [1, 4, 7, 11, 13, 16])
+def test_random_configurations_in_32_bit(seed):
+    """Whole prompt, ragged portions and a mixed batch of a prompt beside a decoding request, for configurations nobody
+    picked by hand."""
+    import random
+
+    c = Case(_random_cfg(random.Random(seed)), "float32", seed=seed, max_num_seqs=3, pool_tokens=1024)
+    toks, short = c.tokens(420, 50 + seed), c.tokens(30, 60 + seed)
+    c.check(c.replay({"w": toks}, [[("w", 420)]]), {"w": toks})
+    c.check(c.replay({"p": toks}, [[("p", n)] for n in _portions(420, [2, 3, 130, 1, 33, 7, 64, 1, 1, 257])]), {"p": toks})
+    mixed = c.replay({"a": toks, "b": short}, [[("a", 300), ("b", 1)]] + [[("a", 1), ("b", 1)] for _ in range(29)] + [[("a", 91)]])
+    c.check(mixed, {"a": toks, "b": short})
+
+
+@pytest.mark.parametrize("seed", [2, 9, 21])
+def test_random_configurations_in_bf16(seed):
+    import random
+
+    c = Case(_random_cfg(random.Random(seed)), "bfloat16", seed=seed, max_num_seqs=2, pool_tokens=512)
+    toks = c.tokens(200, 70 + seed)
+    c.check(c.replay({"p": toks}, [[("p", n)] for n in _portions(200, [40, 2, 1, 1, 65, 17])]), {"p": toks})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype):
+    """280 single tokens after a short prompt: across many chunk borders and pages, with hundreds of keys behind the sigmoid
+    and the differential layers."""
+    c = Case(cfg_b(), dtype, max_num_seqs=2, pool_tokens=512)
+    toks = c.tokens(300, 3)
+    got = c.replay({"x": toks}, [[("x", 20)]] + [[("x", 1)] for _ in range(280)])
+    c.check(got, {"x": toks})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(dtype):
+    """engine.generate: five prompts over three rows, prompts cut by a 48-token budget next to decodes.  Every generated
+    token must be the restatement's argmax given the same history (or lie within rounding noise of it)."""
+    from vllm_neuron_b200.engine import B200Engine
+
+    c = Case(cfg_b(), dtype)
+    eng = B200Engine(c.cfg, c.W, dtype=dtype, max_num_seqs=3, max_pool_tokens=512, max_num_batched_tokens=48)
+    prompts = [c.tokens(n, 20 + n) for n in (70, 3, 33, 1, 100)]
+    outs = eng.generate(prompts, max_new_tokens=12)
+    assert eng.pool.num_free == eng.num_blocks - 1
+    exact = far = 0
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        ref = c.ref(p + o)
+        for k, tok in enumerate(o):
+            row = ref[len(p) + k - 1]
+            best = int(row.argmax())
+            exact += best == tok
+            gap = (row[best] - row[tok]).item() / row.std().item()
+            far += gap > (1e-4 if dtype == "float32" else 0.1)
+    assert far <= (0 if dtype == "float32" else 3) and exact >= (60 if dtype == "float32" else 45), (far, exact)
+
+
+def test_served_from_a_checkpoint_directory_and_layer_streams(tmp_path):
+    """config.json + model.safetensors on disk -> registry -> engine; same logits as the in-memory weights, and the residual
+    stream after every layer equals the restatement's."""
+    import json
+
+    from oracle import zudarax_ref
+    from safetensors.torch import save_file
+    from vllm_neuron_b200.engine import B200Engine
+    from vllm_neuron_b200.registry import load_config
+
+    c = Case(cfg_a(), "float32")
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(c.cfgd, f)
+    save_file({k: v.contiguous() for k, v in c.W.items()}, str(tmp_path / "model.safetensors"))
+    arch, entry, cfg = load_config(str(tmp_path))
+    assert arch == "Zudarax" and entry.family == "hybrid" and cfg == c.cfg
+    eng = B200Engine.from_pretrained(str(tmp_path), dtype="float32", max_num_seqs=2, max_pool_tokens=128)
+    toks = c.tokens(50, 5)
+    cap, fwd = [], eng.model.forward
+    eng.model.forward = lambda tokens, meta, rows: fwd(tokens, meta, rows, capture=cap)
+    got = eng.replay_step([("r", toks, list(range(50)))], ["r"])["r"]
+    assert c.errs(got, toks).max().item() < 1e-4
+    streams = []
+    zudarax_ref.forward(c.cfgd, c.W, toks, capture=streams)
+    assert len(cap) == len(c.cfgd["layers"]) == len(streams)
+    for got_x, want_x in zip(cap, streams):
+        assert (got_x.double().cpu() - want_x).abs().max().item() < 1e-4 * want_x.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_command_line(tmp_path, dtype):
+    """bin/trace_run as a user runs it: a checkpoint folder, steps on standard input (two requests, portions beside single
+    tokens, a step that reports nothing, a request that ends and frees its row), logits files per step."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    from safetensors.torch import save_file
+
+    c = Case(cfg_b(), dtype)
+    model_dir, out_dir = tmp_path / "model", tmp_path / "out"
+    model_dir.mkdir()
+    with open(model_dir / "config.json", "w") as f:
+        json.dump(c.cfgd, f)
+    save_file({k: v.contiguous() for k, v in c.W.items()}, str(model_dir / "model.safetensors"))
+    a, b = c.tokens(70, 31), c.tokens(9, 32)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:33], "want": [0, 32]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[33:35], "want": []}, {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[8:], "want": [0]}, {"id": "a", "tokens": a[35:36], "want": [0]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[36:], "want": [0, 33]}], "end": ["a"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+                        "--out", str(out_dir), "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [ln for ln in p.stdout.splitlines() if ln.startswith("done")] == [f"done {i}" for i in range(4)]
+    ra, rb = c.ref(a), c.ref(b)
+    want = {0: [ra[0], ra[32]], 1: [rb[7]], 2: [rb[8], ra[35]], 3: [ra[36], ra[69]]}
+    for n, rows in want.items():
+        got = np.fromfile(out_dir / f"{n}.f32", dtype="<f4").reshape(len(rows), -1)
+        for g, w in zip(got, rows):
+            d = torch.from_numpy(g).double() - w
+            assert (d - d.mean()).pow(2).mean().sqrt().item() < c.tol * (w - w.mean()).pow(2).mean().sqrt().item()
