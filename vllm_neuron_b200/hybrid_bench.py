@@ -1,5 +1,6 @@
 """Prefill / decode throughput of the hybrid decoders (bench.py --hybrid): the Pumopel design next to the dense Llama decoder
-at equal size (`small`, `1b`), and the Kenetar design next to Pumopel at equal size (`kenetar-small`, `kenetar-1b`).
+at equal size (`small`, `1b`), the Kenetar design next to Pumopel at equal size (`kenetar-small`, `kenetar-1b`), and the
+Zudarax design next to the dense Llama decoder at equal size (`zudarax-small`, `zudarax-1b`).
 
 For each size: random weights, both models in bf16 on one GPU, same width / layer count / vocabulary; the dense model's
 intermediate size equals the hybrid's ACTIVE feed-forward width (top * ff + shared ff) so a token costs about the same FLOPs.
@@ -40,6 +41,63 @@ KENETAR_MIXERS = {
     "small": dict(delta=dict(heads=16, kv_heads=8, dim=64, vdim=64, conv=4),
                   latent=dict(heads=16, dim=64, rot_dim=32, vdim=64, kv_rank=128, q_rank=384)),
 }
+
+
+# the parallel-branch design at the same width / layers / vocabulary: layer pattern 'differential, sigmoid, chunked, differential'
+# repeated, feed-forward width = the dense decoder's intermediate size; the differential layers carry two maps of half a head
+ZUDARAX_MIXERS = {
+    "1b": dict(heads=16, kv_heads=4, dim=128, vdim=128, conv=4, chunk=1024, softcap=30.0),
+    "small": dict(heads=16, kv_heads=4, dim=64, vdim=64, conv=4, chunk=512, softcap=30.0),
+}
+
+
+def zudarax_config(name: str):
+    from .hybrid import HybridConfig
+
+    sz, a = SIZES[name], ZUDARAX_MIXERS[name]
+    ff = {"kind": "dense", "ff": dense_shape(sz).intermediate}
+    base = {"heads": a["heads"], "kv_heads": a["kv_heads"], "vdim": a["vdim"], "scale": a["dim"] ** -0.5}
+    yarn = {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}
+    chunked = {"type": "attention", "mlp": ff, "mixer": dict(base, dim=a["dim"], conv=a["conv"], softcap=a["softcap"],
+                                                            mask={"size": a["chunk"]}, rot={"dims": a["dim"] // 2, "base": 10000.0})}
+    diff = {"type": "attention_2", "mlp": ff, "mixer": dict(base, dim=a["dim"] // 2, diff=0.5, rot={"dims": a["dim"] // 2, "base": 10000.0})}
+    sig = {"type": "attention_3", "mlp": ff, "mixer": dict(base, dim=a["dim"], conv=a["conv"],
+                                                          rot={"dims": a["dim"], "base": 10000.0, "scaling": yarn})}
+    layers = [(diff, sig, chunked, diff)[i % 4] for i in range(sz["layers"])]
+    return HybridConfig.from_dict({"architecture": "Zudarax", "vocab": sz["vocab"], "width": sz["width"],
+                                   "norm": {"eps": 1e-6, "groups": 4}, "layers": layers})
+
+
+def _zudarax_floors(name, t, s_pre, ctx, b, prefill):
+    """Algorithmic (flops, bytes) per launch of the parallel-branch design's own kernels at `t` tokens."""
+    sz, a = SIZES[name], ZUDARAX_MIXERS[name]
+    w, h, g, d, dv, ff = sz["width"], a["heads"], a["kv_heads"], a["dim"], a["vdim"], dense_shape(sz).intermediate
+    c = (h + g) * d + g * dv
+
+    def att(keys_per_query, kv_tokens, maps=1):
+        dm = d // maps  # two maps of half a head: the scores cost the same, the value product is done per map
+        return (2.0 * t * h * maps * keys_per_query * (dm + dv),
+                2.0 * kv_tokens * g * (d + dv) + t * h * maps * (4 * dm + (4 if maps > 1 else 2) * dv))
+
+    ck = a["chunk"]
+    if prefill:
+        full, chk, kv_full, kv_chk = s_pre / 2, min(ck, s_pre) / 2, s_pre, s_pre
+    else:
+        full, chk, kv_full, kv_chk = ctx + 1, ctx % ck + 1, b * (ctx + 1), b * (ctx % ck + 1)
+    out = {}
+    for kern in ("swa_sink_attn_prefill", "swa_sink_attn"):
+        out[kern + "[chunk+cap]"] = att(chk, kv_chk)
+        out[kern + "[sigmoid]"] = att(full, kv_full)
+        out[kern + "[maps]"] = att(full, kv_full, 2)
+    out.update({
+        "causal_conv": (0.0, t * 8.0 * c),
+        "qk_norm_rope_kv_write": (0.0, t * (4.0 * c + 4.0 * h * d + 2.0 * g * (d + dv))),
+        "diff_head_norm_gate": (0.0, t * h * dv * (8 + 2.0)),
+        "poly_norm": (0.0, t * ff * 6.0),
+        "add_group_rmsnorm": (0.0, t * w * (4 + 4 + 4 + 4 + 2.0)),
+        "embed_scale": (0.0, t * w * 6.0),
+    })
+    return out
 
 
 def kenetar_config(name: str):
@@ -233,12 +291,14 @@ def run(args):
     flush = torch.empty(192 << 20, dtype=torch.float32, device=dev)  # 768 MB > L2
     names = list(SIZES) if args.hybrid == "all" else [args.hybrid]
     for name in names:
-        kenetar = name.startswith("kenetar-")
-        sz = SIZES[name[len("kenetar-"):] if kenetar else name]
+        kenetar, zudarax = name.startswith("kenetar-"), name.startswith("zudarax-")
+        short = name.split("-", 1)[1] if kenetar or zudarax else name
+        sz = SIZES[short]
         cfg = hybrid_config(sz)
         s_pre, b, ctx = sz["prefill"], sz["batch"], sz["ctx"]
         bs = 32
-        res = {"metric": "kenetar_vs_pumopel_tokens_per_s" if kenetar else "hybrid_vs_dense_tokens_per_s", "size": name,
+        res = {"metric": "kenetar_vs_pumopel_tokens_per_s" if kenetar else "zudarax_vs_dense_tokens_per_s" if zudarax else
+               "hybrid_vs_dense_tokens_per_s", "size": name,
                "dtype": "bf16", "data": "synthetic (random weights)",
                "roofline_peaks": {"hbm_gbs": hbm / 1e9, "bf16_tflops": peak / 1e12, "source": src},
                "config": {"width": sz["width"], "layers": sz["layers"], "prefill_tokens": s_pre, "decode_batch": b,
@@ -247,7 +307,6 @@ def run(args):
         pum_floors = lambda t, pre: _floors(cfg, sz, t, min(win, s_pre / 2) if pre else min(win, ctx + 1),  # noqa: E731
                                             s_pre if pre else b * min(win, ctx + 1), 1 if pre else b)
         if kenetar:
-            short = name[len("kenetar-"):]
             ken_floors = lambda t, pre: _kenetar_floors(short, t, s_pre / 2 if pre else ctx + 1,  # noqa: E731
                                                         s_pre if pre else b * (ctx + 1), 1 if pre else b)
             res["kenetar"] = _time_hybrid(kenetar_config(short), sz, args, ken_floors, flush, hbm, peak)[0]
@@ -256,7 +315,11 @@ def run(args):
             print(json.dumps(res), flush=True)
             continue
         # ---------------- hybrid
-        res["hybrid"], rows, nblocks, mml, ptoks, dtoks = _time_hybrid(cfg, sz, args, pum_floors, flush, hbm, peak)
+        if zudarax:
+            zud_floors = lambda t, pre: _zudarax_floors(short, t, s_pre, ctx, b, pre)  # noqa: E731
+            res["zudarax"], rows, nblocks, mml, ptoks, dtoks = _time_hybrid(zudarax_config(short), sz, args, zud_floors, flush, hbm, peak)
+        else:
+            res["hybrid"], rows, nblocks, mml, ptoks, dtoks = _time_hybrid(cfg, sz, args, pum_floors, flush, hbm, peak)
         per = -(-mml // bs)
         # ---------------- dense decoder of equal size
         shape = dense_shape(sz)

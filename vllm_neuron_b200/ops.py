@@ -757,11 +757,14 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
     out = torch.empty((t, num_heads * dv), dtype=torch.float32 if out_f32 else k_pool.dtype, device=q_src.device)
     variant = (int(chunk), float(softcap), _ptr(sigmoid_bias), v_div, 1 if out_f32 else 0)
     plain = not chunk and not softcap and sigmoid_bias is None and v_div == 1 and not out_f32
+    # the per-launch timer tells the variants apart (their floors differ)
+    tag = "" if plain else "[" + "+".join(n for n, on in (("chunk", chunk), ("cap", softcap), ("sigmoid", sigmoid_bias is not None),
+                                                            ("maps", v_div > 1)) if on) + "]"
     # prompt portions in bf16 serving: the tensor-core kernel; decode-sized steps, fp32 pools and odd head sizes: one CTA per
     # (token, head) on the CUDA cores
     if (k_pool.dtype == torch.bfloat16 and meta.max_new >= PREFILL_ATTN_MIN_TOKENS and d % 16 == 0 and dv % 16 == 0
             and d <= 512 and dv <= 256 and q_src.stride(0) % 2 == 0):
-        with _k("swa_sink_attn_prefill"):
+        with _k("swa_sink_attn_prefill" + tag):
             check(_cabi.load().b200_swa_sink_attn_prefill(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                                           block_table.stride(0), _ptr(meta.seq_start), _ptr(meta.seq_slot),
                                                           _ptr(meta.seq_pos0), meta.num_seqs, meta.max_new, _ptr(sink), float(scale),
@@ -777,7 +780,7 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
                                                        block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos), float(scale),
                                                        _ptr(out), t, num_heads, d, dv, bs, _stream()), "b200_latent_attn_decode")
         return out
-    with _k("swa_sink_attn"):
+    with _k("swa_sink_attn" + tag):
         check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
                                               _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
                                               _ptr(sink), float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, v_pitch, bs,
