@@ -30,9 +30,10 @@ __global__ void __launch_bounds__(128)
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                             const int32_t* __restrict__ seq_pos0, const float* __restrict__ sink, float scale, int window,
                             void* __restrict__ out, int H, int G, int D, int Dv, int bs, int v_pitch, int chunk, float softcap,
-                            const float* __restrict__ sig_bias, int v_div, int out_f32, int split_p) {
+                            const float* __restrict__ sig_bias, int v_div, int out_f32, int split_p, int bs_shift) {
   griddep_wait();
-  const int sq = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * PF_ROWS;
+  // the last rows of a portion see the most keys: their tiles are launched first, so the longest CTAs do not form the tail
+  const int sq = blockIdx.z, h = blockIdx.y, i0 = (gridDim.x - 1 - blockIdx.x) * PF_ROWS;
   const int t0 = seq_start[sq], n = seq_start[sq + 1] - t0;
   if (i0 >= n) return;
   extern __shared__ __align__(16) unsigned char smraw[];
@@ -60,6 +61,14 @@ __global__ void __launch_bounds__(128)
   const int r_lo = 16 * warp + (lane >> 2);
   const int p_lo = pos0 + i0 + r_lo, p_hi = p_lo + 8;
   const bool ok_lo = i0 + r_lo < n, ok_hi = i0 + r_lo + 8 < n;
+  // first key a position sees: the window's and the chunk's lower bounds (both grow with the position)
+  auto lower = [&](int pos) {
+    int lb = pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (chunk > 0 && pos - pos % chunk > lb) lb = pos - pos % chunk;
+    return lb;
+  };
+  const int lb_lo = lower(p_lo), lb_hi = lower(p_hi);
+  const int w_first = pos0 + i0 + 16 * warp, w_lb = lower(w_first + 15);  // the warp's first position, its last row's bound
   float m_lo = sig ? 0.f : sink ? sink[h] : -INFINITY, m_hi = m_lo;
   float l_lo = sink && (lane & 3) == 0 ? 1.0f : 0.f, l_hi = l_lo;  // the sink's share of the denominator, counted once per row
   float o[2 * DV16M][4];
@@ -73,18 +82,22 @@ __global__ void __launch_bounds__(128)
   if (chunk > 0 && first_pos - first_pos % chunk > j_lo) j_lo = first_pos - first_pos % chunk;
   const int j_hi = first_pos + last_row;  // inclusive
   const int kch = D / 8, vch = v_alias ? 0 : Dv / 8;  // 16-byte chunks per row
-  // one tile of 32 keys (K and V rows, page by page through the block table) into stage `st`; rows past j_hi are zeros
+  // one tile of 32 keys (K and V rows, page by page through the block table) into stage `st`; rows past j_hi are zeros.
+  // Four threads share a row and take its 16-byte chunks in turn, so the page look-up happens once per thread and tile.
+  constexpr int TPR = 128 / PF_KEYS;
+  const int ir = tid / TPR, ic = tid % TPR;
   auto issue = [&](int j0, int st) {
-    __nv_bfloat16* Kd = Ks0 + st * PF_KEYS * ldk;
-    __nv_bfloat16* Vd = Vs0 + st * PF_KEYS * ldv;
-    for (int i = tid; j0 <= j_hi && i < PF_KEYS * (kch + vch); i += 128) {
-      const int r = i / (kch + vch), c = i - r * (kch + vch);
-      const int j = j0 + r;
+    if (j0 <= j_hi) {
+      const int j = j0 + ir;
       const bool ok = j <= j_hi;
-      const int64_t blk = ok ? bt[j / bs] : 0;
-      const int64_t row = ok ? (blk * G + g) * bs + (j % bs) : 0, vrow = ok ? (blk * Gv + gv) * bs + (j % bs) : 0;
-      if (c < kch) cp_async16(smem_u32(Kd + r * ldk + c * 8), k_pool + row * D + c * 8, ok);
-      else cp_async16(smem_u32(Vd + r * ldv + (c - kch) * 8), v_pool + vrow * v_pitch + (c - kch) * 8, ok);
+      const int page = ok ? (bs_shift >= 0 ? j >> bs_shift : j / bs) : 0;
+      const int off = ok ? j - page * bs : 0;
+      const int64_t blk = ok ? bt[page] : 0;
+      const __nv_bfloat16* kr = k_pool + ((blk * G + g) * bs + off) * D;
+      const __nv_bfloat16* vr = v_pool + ((blk * Gv + gv) * bs + off) * v_pitch;
+      const uint32_t kd = smem_u32(Ks0 + (st * PF_KEYS + ir) * ldk), vd = smem_u32(Vs0 + (st * PF_KEYS + ir) * ldv);
+      for (int c = ic; c < kch; c += TPR) cp_async16(kd + c * 16, kr + c * 8, ok);
+      for (int c = ic; c < vch; c += TPR) cp_async16(vd + c * 16, vr + c * 8, ok);
     }
     cp_async_commit();  // an empty group past the last tile keeps the wait counts uniform
   };
@@ -117,23 +130,34 @@ __global__ void __launch_bounds__(128)
         mma_bf16_16816(s[2 * jp + 1], af, bf[2], bf[3]);
       }
     }
-    // ---- mask, online softmax (fp32)
+    // ---- mask, online softmax (fp32).  A tile that every row of the warp sees whole (all its keys at or before the warp's
+    // first row, none before the lower bound of its last row; the bounds grow with the position) skips the per-element mask
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
+    const bool whole = j0 + PF_KEYS - 1 <= w_first && j0 >= w_lb;
+    if (whole && !sig && softcap <= 0.f) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
-        const bool hi = c >= 2;
-        const int pos = hi ? p_hi : p_lo;
-        const bool seen = (hi ? ok_hi : ok_lo) && key <= pos && pos - key < window && (chunk <= 0 || key >= pos - pos % chunk);
-        float v = s[j][c] * scale;
-        if (softcap > 0.f) v = softcap * tanhf(v / softcap);
-        if (sig) v = seen ? 1.0f / (1.0f + __expf(-(v + sb))) : 0.f;  // the weight itself
-        else if (!seen) v = -INFINITY;
-        s[j][c] = v;
-        if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+      for (int j = 0; j < 4; ++j) {
+        s[j][0] *= scale, s[j][1] *= scale, s[j][2] *= scale, s[j][3] *= scale;
+        mx_lo = fmaxf(mx_lo, fmaxf(s[j][0], s[j][1]));
+        mx_hi = fmaxf(mx_hi, fmaxf(s[j][2], s[j][3]));
       }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
+          const bool hi = c >= 2;
+          const int pos = hi ? p_hi : p_lo;
+          const bool seen = whole || ((hi ? ok_hi : ok_lo) && key <= pos && key >= (hi ? lb_hi : lb_lo));
+          float v = s[j][c] * scale;
+          if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+          if (sig) v = seen ? 1.0f / (1.0f + __expf(-(v + sb))) : 0.f;  // the weight itself
+          else if (!seen) v = -INFINITY;
+          s[j][c] = v;
+          if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+        }
+    }
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
@@ -166,12 +190,14 @@ __global__ void __launch_bounds__(128)
         pr[j][1] = pack_bf16(p2 - h1.x, p3 - h1.y);
       }
     }
+    if (c_lo != 1.0f || c_hi != 1.0f) {  // a maximum that did not move leaves the accumulators as they are
 #pragma unroll
-    for (int j = 0; j < 2 * DV16M; ++j) {
-      o[j][0] *= c_lo;
-      o[j][1] *= c_lo;
-      o[j][2] *= c_hi;
-      o[j][3] *= c_hi;
+      for (int j = 0; j < 2 * DV16M; ++j) {
+        o[j][0] *= c_lo;
+        o[j][1] *= c_lo;
+        o[j][2] *= c_hi;
+        o[j][3] *= c_hi;
+      }
     }
     // ---- O += P V: keys are the contraction (two k16 steps), V rows read transposed
 #pragma unroll
@@ -246,6 +272,9 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
   dim3 grid((max_new + PF_ROWS - 1) / PF_ROWS, H, B);
   const size_t smem = ((size_t)(PF_ROWS + PF_STAGES * PF_KEYS) * (D + 8) + (v_pool == k_pool ? 0 : (size_t)PF_STAGES * PF_KEYS * (Dv + 8))) * 2;
   cudaStream_t st = (cudaStream_t)stream;
+  int bs_shift = -1;  // pages of a power of two: shifts instead of divisions in the gather
+  for (int k = 0; k < 16; ++k)
+    if (block_size == 1 << k) bs_shift = k;
   typedef __nv_bfloat16 BT;
 #define PF_LAUNCH(M)                                                                                                          \
   do {                                                                                                                        \
@@ -253,7 +282,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
       B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_prefill_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     B200_CUDA_OK(launch_kernel(swa_sink_prefill_kernel<M>, grid, dim3(128), smem, st, q, ldq, (const BT*)k_pool,              \
                                (const BT*)v_pool, block_table, bt_stride, seq_start, seq_slot, seq_pos0, sink, scale, window, \
-                               out, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p));         \
+                               out, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p, bs_shift)); \
   } while (0)
   if (Dv <= 64) PF_LAUNCH(4);
   else if (Dv <= 128) PF_LAUNCH(8);
