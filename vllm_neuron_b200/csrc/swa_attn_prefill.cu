@@ -20,11 +20,12 @@ namespace b200 {
 
 constexpr int PF_ROWS = 64;
 constexpr int PF_KEYS = 32;
+constexpr int PF_NT = PF_KEYS / 8;  // n8 score tiles per key tile
 constexpr int PF_STAGES = 2;  // ring of K / V tiles: the next tile's cp.async copies run under the current tile's MMAs (a third
                               // stage costs a resident CTA per SM and measured slower)
 
 template <int DV16M>  // accumulator capacity: Dv <= 16 * DV16M
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, DV16M <= 8 ? 4 : 2)
     swa_sink_prefill_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
                             const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(128)
   const int Gv = G / v_div, gv = g / v_div;
   const bool sig = sig_bias != nullptr;
   const float sb = sig ? sig_bias[h] : 0.f;
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   const int pos0 = seq_pos0[sq];
   const int32_t* bt = block_table + (int64_t)seq_slot[sq] * bt_stride;
   // ---- Q tile: fp32 rows -> bf16 shared memory (rows past the portion are zero)
@@ -86,13 +88,17 @@ __global__ void __launch_bounds__(128)
   // Four threads share a row and take its 16-byte chunks in turn, so the page look-up happens once per thread and tile.
   constexpr int TPR = 128 / PF_KEYS;
   const int ir = tid / TPR, ic = tid % TPR;
-  auto issue = [&](int j0, int st) {
+  // the page of this thread's row in the tile at j0 (looked up one tile before the copies that need it are issued)
+  auto page_of = [&](int j0) -> int64_t {
+    const int j = j0 + ir;
+    if (j > j_hi) return 0;
+    return bt[bs_shift >= 0 ? j >> bs_shift : j / bs];
+  };
+  auto issue = [&](int j0, int st, int64_t blk) {
     if (j0 <= j_hi) {
       const int j = j0 + ir;
       const bool ok = j <= j_hi;
-      const int page = ok ? (bs_shift >= 0 ? j >> bs_shift : j / bs) : 0;
-      const int off = ok ? j - page * bs : 0;
-      const int64_t blk = ok ? bt[page] : 0;
+      const int off = ok ? (bs_shift >= 0 ? j & (bs - 1) : j % bs) : 0;
       const __nv_bfloat16* kr = k_pool + ((blk * G + g) * bs + off) * D;
       const __nv_bfloat16* vr = v_pool + ((blk * Gv + gv) * bs + off) * v_pitch;
       const uint32_t kd = smem_u32(Ks0 + (st * PF_KEYS + ir) * ldk), vd = smem_u32(Vs0 + (st * PF_KEYS + ir) * ldv);
@@ -102,27 +108,30 @@ __global__ void __launch_bounds__(128)
     cp_async_commit();  // an empty group past the last tile keeps the wait counts uniform
   };
   const int j_first = (j_lo / PF_KEYS) * PF_KEYS;
-#pragma unroll
-  for (int s = 0; s < PF_STAGES - 1; ++s) issue(j_first + s * PF_KEYS, s);
+  static_assert(PF_STAGES == 2, "the page look-ahead below is written for two stages");
+  issue(j_first, 0, page_of(j_first));
+  int64_t blk_next = page_of(j_first + PF_KEYS);
   for (int j0 = j_first, it = 0; j0 <= j_hi; j0 += PF_KEYS, ++it) {
     const int st = it % PF_STAGES;
     // refill the stage that the barrier at the end of the previous tile released, then wait for this tile's group
-    issue(j0 + (PF_STAGES - 1) * PF_KEYS, (it + PF_STAGES - 1) % PF_STAGES);
+    issue(j0 + PF_KEYS, (it + 1) % PF_STAGES, blk_next);
+    blk_next = page_of(j0 + 2 * PF_KEYS);
     cp_async_wait<PF_STAGES - 1>();
     __syncthreads();  // this tile's copies of every thread have landed (and, first time, Q is written)
     const __nv_bfloat16* Ks = Ks0 + st * PF_KEYS * ldk;
     const __nv_bfloat16* Vs = Vs0 + st * PF_KEYS * ldv;
     // ---- S = Q K^T: 16 rows x 32 keys per warp
-    float s[4][4];
+    float s[PF_NT][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < PF_NT; ++j)
 #pragma unroll
       for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+#pragma unroll 2
     for (int kk = 0; kk < D; kk += 16) {
       uint32_t af[4];
       ldmatrix_x4(af, smem_u32(Qs + (16 * warp + (lane & 15)) * ldk + kk + (lane >> 4) * 8));
 #pragma unroll
-      for (int jp = 0; jp < 2; ++jp) {
+      for (int jp = 0; jp < PF_NT / 2; ++jp) {
         uint32_t bf[4];
         const int mi = lane >> 3;
         ldmatrix_x4(bf, smem_u32(Ks + (16 * jp + (mi >> 1) * 8 + (lane & 7)) * ldk + kk + (mi & 1) * 8));
@@ -136,14 +145,14 @@ __global__ void __launch_bounds__(128)
     const bool whole = j0 + PF_KEYS - 1 <= w_first && j0 >= w_lb;
     if (whole && !sig && softcap <= 0.f) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < PF_NT; ++j) {
         s[j][0] *= scale, s[j][1] *= scale, s[j][2] *= scale, s[j][3] *= scale;
         mx_lo = fmaxf(mx_lo, fmaxf(s[j][0], s[j][1]));
         mx_hi = fmaxf(mx_hi, fmaxf(s[j][2], s[j][3]));
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < PF_NT; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
@@ -151,8 +160,9 @@ __global__ void __launch_bounds__(128)
           const int pos = hi ? p_hi : p_lo;
           const bool seen = whole || ((hi ? ok_hi : ok_lo) && key <= pos && key >= (hi ? lb_hi : lb_lo));
           float v = s[j][c] * scale;
-          if (softcap > 0.f) v = softcap * tanhf(v / softcap);
-          if (sig) v = seen ? 1.0f / (1.0f + __expf(-(v + sb))) : 0.f;  // the weight itself
+          // tanh(x) = 1 - 2 / (1 + e^(2x)): absolute error ~1e-7, so the capped score is good to ~1e-7 of the cap
+          if (softcap > 0.f) v = softcap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v * inv_cap)));
+          if (sig) v = seen ? __fdividef(1.0f, 1.0f + __expf(-(v + sb))) : 0.f;  // the weight itself
           else if (!seen) v = -INFINITY;
           s[j][c] = v;
           if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
@@ -169,9 +179,9 @@ __global__ void __launch_bounds__(128)
     m_hi = mn_hi;
     l_lo *= c_lo;
     l_hi *= c_hi;
-    uint32_t pf[4][2], pr[4][2];  // P as bf16 pairs: [n8 tile][row half]; pr = what bf16 rounding left over (split_p)
+    uint32_t pf[PF_NT][2], pr[PF_NT][2];  // P as bf16 pairs: [n8 tile][row half]; pr = what bf16 rounding left over (split_p)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < PF_NT; ++j) {
       float p0, p1, p2, p3;
       if (sig) {
         p0 = s[j][0], p1 = s[j][1], p2 = s[j][2], p3 = s[j][3];
@@ -201,7 +211,7 @@ __global__ void __launch_bounds__(128)
     }
     // ---- O += P V: keys are the contraction (two k16 steps), V rows read transposed
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
+    for (int ks = 0; ks < PF_NT / 2; ++ks) {
       const uint32_t af[4] = {pf[2 * ks][0], pf[2 * ks][1], pf[2 * ks + 1][0], pf[2 * ks + 1][1]};
       const uint32_t ar[4] = {pr[2 * ks][0], pr[2 * ks][1], pr[2 * ks + 1][0], pr[2 * ks + 1][1]};
 #pragma unroll
