@@ -345,11 +345,14 @@ int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* 
  * Variants: chunk > 0 also hides keys before the first position of the query's chunk, pos - pos % chunk; softcap > 0 replaces
  * the scaled score s by softcap * tanh(s / softcap); sigmoid_bias fp32 [H] (or NULL) makes the weight of a visible key
  * sigmoid(s + sigmoid_bias[h]) with no normalisation over keys (no sink then); v_div >= 1: key head g reads value head
- * g / v_div of a value pool with G / v_div heads; out_f32: fp32 output rows whatever kv_dtype. */
+ * g / v_div of a value pool with G / v_div heads; out_f32: fp32 output rows whatever kv_dtype.
+ * splits > 1: that many CTAs share a (token, head block)'s keys and a second launch merges their partial results from
+ * split_workspace fp32 [T * H * splits * (Dv + 2)] (long contexts at small batch: more CTAs than one per token and head block). */
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
                        int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
-                       float softcap, const float* sigmoid_bias, int v_div, int out_f32, void* stream);
+                       float softcap, const float* sigmoid_bias, int v_div, int out_f32, int splits, float* split_workspace,
+                       void* stream);
 /* The same attention for prompt portions on the tensor cores (bf16 pools; D and Dv multiples of 16, Dv <= 256, else
  * B200_ERR_UNSUPPORTED): sequence s brings tokens [seq_start[s], seq_start[s+1]) at positions seq_pos0[s].., block-table row
  * seq_slot[s]; max_new = the longest portion of the step.  q is rounded to bf16; softmax and accumulation are fp32.
@@ -360,6 +363,18 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
                                int Dv, int v_pitch, int block_size, int chunk, float softcap, const float* sigmoid_bias, int v_div,
                                int out_f32, int split_p, void* stream);
+/* The same attention for decode-sized steps on the tensor cores (bf16 pools with a value pool of its own; D and Dv multiples of
+ * 16, Dv <= 256, else B200_ERR_UNSUPPORTED): the query heads of a kv head are the rows of one MMA tile, each key and value row
+ * is fetched once for all of them.  Arguments as b200_swa_sink_attn (+ split_p as in the prompt kernel). */
+int b200_swa_sink_attn_decode_tc(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                                 int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
+                                 int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
+                                 float softcap, const float* sigmoid_bias, int v_div, int out_f32, int split_p, int splits,
+                                 float* split_workspace, void* stream);
+/* Merge of key splits: part fp32 [rows][splits][2 + Dv] = {maximum, denominator, unnormalised accumulator} per split ->
+ * out [rows][Dv] (fp32 when out_f32, else out_dtype); sigmoid: plain sums, no denominator. */
+int b200_attn_split_merge(const float* part, int splits, int Dv, int sigmoid, int out_f32, int out_dtype, void* out, int64_t rows,
+                          void* stream);
 /* Between the projections and the attention of layers that norm and rotate: fp32 rows `src` (pitch ld) hold q [H][D] at
  * q_col0, k [G][D] at k_col0, v [Gv][Dv] at v_col0.  q_norm / k_norm fp32 [H * D] / [G * D] (or NULL): RMS norm over the WHOLE
  * projection, times the weight.  The first rot_n columns of every q and k head turn by tok_pos[t]: pairs (i, i + rot_n / 2) when

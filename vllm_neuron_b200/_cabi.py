@@ -80,9 +80,12 @@ SIGNATURES = {
     "b200_kv_write_vmix": (_i, [_p, _i, _i, _i, _p, _f, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "b200_causal_conv": (_i, [_p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "b200_swa_sink_attn": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _i,
-                                _p]),
+                                _i, _p, _p]),
     "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _f,
                                         _p, _i, _i, _i, _p]),
+    "b200_swa_sink_attn_decode_tc": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i,
+                                          _i, _i, _i, _p, _p]),
+    "b200_attn_split_merge": (_i, [_p, _i, _i, _i, _i, _i, _p, _i64, _p]),
     "b200_qk_norm_rope_kv_write": (_i, [_p, _i, _i, _i, _i, _p, _p, _f, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i,
                                         _i, _i, _p]),
     "b200_moe_topk": (_i, [_p, _i, _p, _i, _p, _p, _i, _i, _i, _p]),

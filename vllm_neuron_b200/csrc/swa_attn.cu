@@ -216,10 +216,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                          const int32_t* __restrict__ block_table, int64_t bt_stride, const int32_t* __restrict__ tok_row,
                          const int32_t* __restrict__ tok_pos, const float* __restrict__ sink, float scale, int window,
                          void* __restrict__ out, int T, int H, int G, int D, int Dv, int bs, int v_pitch, int chunk, float softcap,
-                         const float* __restrict__ sig_bias, int v_div, int out_f32) {
+                         const float* __restrict__ sig_bias, int v_div, int out_f32, float* __restrict__ part) {
   griddep_launch();
   griddep_wait();
   extern __shared__ __align__(16) float sm_att[];
+  // gridDim.y CTAs split a (token, head block)'s keys: key tiles go round-robin over (split, warp); with more than one
+  // split the CTA leaves its maximum, denominator and unnormalised accumulator in `part` for attn_split_merge_kernel
+  const int split = blockIdx.y, splits = gridDim.y;
   const int Dp = (D + 3) & ~3;                    // pitch of a query row: 16-byte aligned rows
   float* qs = sm_att;                             // [QH][Dp]
   float* accs = qs + QH * Dp;                     // [ATT_WARPS][QH][64 MAXC]
@@ -245,11 +248,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 #pragma unroll
   for (int qh = 0; qh < QH; ++qh) {
     m[qh] = sig ? 0.f : sink ? sink[h0 + qh] : -INFINITY;
-    l[qh] = sink && warp == 0 ? 1.0f : 0.f;
+    l[qh] = sink && warp == 0 && split == 0 ? 1.0f : 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) acc[qh][c] = make_float2(0.f, 0.f);
   }
-  for (int j0 = lo + 32 * warp; j0 <= pos; j0 += 32 * ATT_WARPS) {
+  for (int j0 = lo + 32 * (warp + ATT_WARPS * split); j0 <= pos; j0 += 32 * ATT_WARPS * splits) {
     const int j = j0 + lane;
     const bool valid = j <= pos;
     int64_t tile = 0, vtile = 0;  // row index of (block, kv head, token) in the key / value pool
@@ -328,13 +331,42 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     const int c = d >> 6, e = d & 63;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) {
-      const float f = expf(ml[2 * (w * QH + qh)] - mt);
+      const float f = mt == -INFINITY ? 0.f : expf(ml[2 * (w * QH + qh)] - mt);  // a split that saw no key at all
       lt += ml[2 * (w * QH + qh) + 1] * f;
       v += accs[((w * QH + qh) * MAXC + c) * 64 + e] * f;
+    }
+    if (splits > 1) {
+      float* pr = part + (((int64_t)t * H + h0 + qh) * splits + split) * (Dv + 2);
+      if (d == 0) pr[0] = mt, pr[1] = lt;
+      pr[2 + d] = v;
+      continue;
     }
     const float r = sig ? v : v / lt;
     if (out_f32) reinterpret_cast<float*>(out)[((int64_t)t * H + h0 + qh) * Dv + d] = r;
     else stf(reinterpret_cast<KT*>(out), ((int64_t)t * H + h0 + qh) * Dv + d, r);
+  }
+}
+
+// One warp per (token, head): out = sum_s v_s e^(m_s - M) / sum_s l_s e^(m_s - M) over the key splits' partial results
+// [T * H][splits][2 + Dv] = {maximum, denominator, unnormalised accumulator}; sigmoid weights have no denominator.
+template <typename KT>
+__global__ void attn_split_merge_kernel(const float* __restrict__ part, int splits, int Dv, int sig, int out_f32,
+                                        void* __restrict__ out, int64_t rows) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* p = part + r * splits * (Dv + 2);
+  float M = -INFINITY, L = 0.f;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * (Dv + 2)]);
+  for (int s = 0; s < splits; ++s) L += p[s * (Dv + 2) + 1] * expf(p[s * (Dv + 2)] - M);
+  for (int d = lane; d < Dv; d += 32) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += p[s * (Dv + 2) + 2 + d] * expf(p[s * (Dv + 2)] - M);
+    if (!sig) v /= L;
+    if (out_f32) reinterpret_cast<float*>(out)[r * Dv + d] = v;
+    else stf(reinterpret_cast<KT*>(out), r * Dv + d, v);
   }
 }
 
@@ -354,6 +386,16 @@ int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* 
                      B200_CUDA_OK(launch_kernel(kv_write_vmix_kernel<KT>, dim3(T), dim3(128), 0, (cudaStream_t)stream, qkv, ld,
                                                 k_col0, v_col0, v_first, lambda, mode, (KT*)k_pool, (KT*)v_pool, slot_mapping, G, D,
                                                 Dv, block_size)));
+  return B200_OK;
+}
+
+int b200_attn_split_merge(const float* part, int splits, int Dv, int sigmoid, int out_f32, int out_dtype, void* out, int64_t rows,
+                          void* stream) {
+  B200_REQUIRE(part && out && splits >= 1 && Dv >= 1, "attn_split_merge: null pointer or bad shape");
+  if (rows <= 0) return B200_OK;
+  B200_DISPATCH_ELEM(out_dtype, KT,
+                     B200_CUDA_OK(launch_kernel(attn_split_merge_kernel<KT>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0,
+                                                (cudaStream_t)stream, part, splits, Dv, sigmoid, out_f32, out, rows)));
   return B200_OK;
 }
 
@@ -377,13 +419,15 @@ int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0,
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
                        int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
-                       float softcap, const float* sigmoid_bias, int v_div, int out_f32, void* stream) {
+                       float softcap, const float* sigmoid_bias, int v_div, int out_f32, int splits, float* split_workspace,
+                       void* stream) {
   B200_REQUIRE(q && k_pool && v_pool && block_table && tok_row && tok_pos && out, "swa_sink_attn: null pointer");
   B200_REQUIRE(v_pitch >= Dv, "swa_sink_attn: value rows of pitch %d hold %d values", v_pitch, Dv);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "swa_sink_attn: %d query heads over %d kv heads", H, G);
   B200_REQUIRE(window >= 1 && chunk >= 0, "swa_sink_attn: window %d, chunk %d", window, chunk);
   B200_REQUIRE(v_div >= 1 && G % v_div == 0, "swa_sink_attn: %d key heads do not share values %d by %d", G, v_div, v_div);
   B200_REQUIRE(!(sigmoid_bias && sink), "swa_sink_attn: sigmoid weights have no denominator for a sink to join");
+  B200_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || split_workspace), "swa_sink_attn: %d key splits need a workspace", splits);
   B200_REQUIRE(Dv >= 1 && Dv <= 512 && D >= 1 && D <= 1024, "swa_sink_attn: head sizes %d / %d outside 1..1024 / 1..512", D, Dv);
   if (T <= 0) return B200_OK;
   B200_REQUIRE((int64_t)T * H < (1ll << 31), "swa_sink_attn: %d tokens x %d heads exceed the grid", T, H);
@@ -391,7 +435,7 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
   int QHr = rep % 4 == 0 ? 4 : rep % 2 == 0 ? 2 : 1;
   if (Dv > 256 && QHr > 2) QHr = 2;  // accumulator registers: 2 heads x 512 values per lane
   while (QHr > 1 && (int64_t)T * (H / QHr) < 148) QHr /= 2;  // small steps: keep a CTA per SM before sharing key rows
-  dim3 grid((unsigned)(T * (H / QHr)));
+  dim3 grid((unsigned)(T * (H / QHr)), (unsigned)splits);
   cudaStream_t st = (cudaStream_t)stream;
   const int Dp = (D + 3) & ~3;
 #define ATT_LAUNCH_Q(MC, QH)                                                                                                 \
@@ -402,7 +446,8 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
                                         (int)smem));                                                                         \
     B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC, QH>, grid, dim3(ATT_WARPS * 32), smem, st, q, ldq,               \
                                (const KT*)k_pool, (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, \
-                               window, out, T, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32));     \
+                               window, out, T, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32,       \
+                               split_workspace));                                                                           \
   } while (0)
 #define ATT_LAUNCH(MC)                \
   do {                                \
@@ -418,6 +463,8 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
   });
 #undef ATT_LAUNCH_Q
 #undef ATT_LAUNCH
+  if (splits > 1)
+    return b200_attn_split_merge(split_workspace, splits, Dv, sigmoid_bias ? 1 : 0, out_f32, kv_dtype, out, (int64_t)T * H, stream);
   return B200_OK;
 }
 

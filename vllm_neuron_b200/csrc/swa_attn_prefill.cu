@@ -21,6 +21,7 @@ namespace b200 {
 constexpr int PF_ROWS = 64;
 constexpr int PF_KEYS = 32;
 constexpr int PF_NT = PF_KEYS / 8;  // n8 score tiles per key tile
+constexpr int LDT_KEYS = 32;  // keys per warp tile of the decode-sized kernel
 constexpr int PF_STAGES = 2;  // ring of K / V tiles: the next tile's cp.async copies run under the current tile's MMAs (a third
                               // stage costs a resident CTA per SM and measured slower)
 
@@ -258,6 +259,228 @@ __global__ void __launch_bounds__(128, DV16M <= 8 ? 4 : 2)
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Decode-sized steps on the tensor cores (bf16 pools): one CTA per (token, kv head, block of up to 16 of its query heads).  The
+// query heads that share the kv head are the ROWS of the m16 MMA tile, so a key or value row is fetched once for all of them;
+// the CTA's warps take the visible keys in tiles of 32 round-robin, each gathering its tile into its own shared-memory buffer
+// with cp.async (a whole tile in flight per warp: the launch is bound by memory latency, not by arithmetic), and merge through
+// shared memory.  gridDim.y CTAs may split the keys further; their partial results go to `part` (attn_split_merge_kernel).
+// Same variants as the kernels above.
+constexpr int DT_WARPS = 4;
+
+template <int DV16M>
+__global__ void __launch_bounds__(DT_WARPS * 32)
+    swa_sink_decode_tc_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
+                              const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
+                              const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos,
+                              const float* __restrict__ sink, float scale, int window, void* __restrict__ out, int H, int G, int D,
+                              int Dv, int bs, int v_pitch, int chunk, float softcap, const float* __restrict__ sig_bias, int v_div,
+                              int out_f32, int split_p, float* __restrict__ part) {
+  griddep_wait();
+  extern __shared__ __align__(16) unsigned char dt_sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.y, splits = gridDim.y;
+  const int rep = H / G, hbn = (rep + 15) / 16;
+  const int hb = blockIdx.x % hbn, g = (blockIdx.x / hbn) % G, t = blockIdx.x / (hbn * G);
+  const int h0 = g * rep + hb * 16, nrow = rep - hb * 16 < 16 ? rep - hb * 16 : 16;  // this CTA's heads h0 .. h0 + nrow
+  const int Gv = G / v_div, gv = g / v_div;
+  const bool sig = sig_bias != nullptr;
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
+  const int ldk = D + 8, ldv = Dv + 8, wbuf = LDT_KEYS * (ldk + ldv);
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(dt_sm);             // [16][ldk]
+  __nv_bfloat16* Kt = Qs + 16 * ldk + (size_t)warp * wbuf;                  // this warp's [32][ldk] keys, then [32][ldv] values
+  __nv_bfloat16* Vt = Kt + LDT_KEYS * ldk;
+  float* ml = reinterpret_cast<float*>(Qs + 16 * ldk + (size_t)DT_WARPS * wbuf);  // [warps][16][2]
+  const int pos = tok_pos[t];
+  const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
+  for (int i = threadIdx.x; i < 16 * (D / 2); i += DT_WARPS * 32) {
+    const int r = i / (D / 2), d = (i - r * (D / 2)) * 2;
+    float2 v = make_float2(0.f, 0.f);
+    if (r < nrow) v = *reinterpret_cast<const float2*>(q + (int64_t)t * ldq + (int64_t)(h0 + r) * D + d);
+    *reinterpret_cast<__nv_bfloat162*>(Qs + r * ldk + d) = __floats2bfloat162_rn(v.x, v.y);
+  }
+  __syncthreads();
+  int lo = pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (chunk > 0 && pos - pos % chunk > lo) lo = pos - pos % chunk;
+  const int r_lo = lane >> 2;
+  const bool ok_lo = r_lo < nrow, ok_hi = r_lo + 8 < nrow;
+  const float sb_lo = sig && ok_lo ? sig_bias[h0 + r_lo] : 0.f, sb_hi = sig && ok_hi ? sig_bias[h0 + r_lo + 8] : 0.f;
+  float m_lo = sig ? 0.f : sink && ok_lo ? sink[h0 + r_lo] : -INFINITY;
+  float m_hi = sig ? 0.f : sink && ok_hi ? sink[h0 + r_lo + 8] : -INFINITY;
+  const bool count_sink = sink && warp == 0 && split == 0 && (lane & 3) == 0;  // the sink's 1 in the denominator, once per row
+  float l_lo = count_sink && ok_lo ? 1.0f : 0.f, l_hi = count_sink && ok_hi ? 1.0f : 0.f;
+  float o[2 * DV16M][4];
+#pragma unroll
+  for (int j = 0; j < 2 * DV16M; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[j][c] = 0.f;
+  const int kch = D / 8, vch = Dv / 8;  // 16-byte chunks per row
+  for (int j0 = lo + LDT_KEYS * (warp + DT_WARPS * split); j0 <= pos; j0 += LDT_KEYS * DT_WARPS * splits) {
+    // ---- this warp's 32 key and value rows -> its buffer (rows past the token's position are zeros)
+    const int jm = j0 + lane;
+    int64_t my_k = -1, my_v = -1;
+    if (jm <= pos) {
+      const int64_t blk = bt[jm / bs];
+      my_k = (blk * G + g) * bs + (jm % bs);
+      my_v = (blk * Gv + gv) * bs + (jm % bs);
+    }
+    for (int r = 0; r < LDT_KEYS; ++r) {
+      const int64_t kr = __shfl_sync(0xffffffffu, my_k, r), vr = __shfl_sync(0xffffffffu, my_v, r);
+      const bool ok = kr >= 0;
+      for (int c = lane; c < kch + vch; c += 32) {
+        if (c < kch) cp_async16(smem_u32(Kt + r * ldk + c * 8), k_pool + (ok ? kr : 0) * D + c * 8, ok);
+        else cp_async16(smem_u32(Vt + r * ldv + (c - kch) * 8), v_pool + (ok ? vr : 0) * v_pitch + (c - kch) * 8, ok);
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+    // ---- S = Q K^T: 16 heads x 32 keys
+    float s[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+#pragma unroll 2
+    for (int kk = 0; kk < D; kk += 16) {
+      uint32_t af[4];
+      ldmatrix_x4(af, smem_u32(Qs + (lane & 15) * ldk + kk + (lane >> 4) * 8));
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {
+        uint32_t bf[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4(bf, smem_u32(Kt + (16 * jp + (mi >> 1) * 8 + (lane & 7)) * ldk + kk + (mi & 1) * 8));
+        mma_bf16_16816(s[2 * jp], af, bf[0], bf[1]);
+        mma_bf16_16816(s[2 * jp + 1], af, bf[2], bf[3]);
+      }
+    }
+    // ---- mask (every row is the same token: keys lo .. pos are visible), weights in fp32
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
+        const bool hi = c >= 2, seen = key <= pos;
+        float v = s[j][c] * scale;
+        if (softcap > 0.f) v = softcap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v * inv_cap)));
+        if (sig) v = seen ? __fdividef(1.0f, 1.0f + __expf(-(v + (hi ? sb_hi : sb_lo)))) : 0.f;
+        else if (!seen) v = -INFINITY;
+        s[j][c] = v;
+        if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+      }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = sig ? 0.f : fmaxf(m_lo, mx_lo), mn_hi = sig ? 0.f : fmaxf(m_hi, mx_hi);  // finite: key j0 is visible
+    const float c_lo = __expf(m_lo - mn_lo), c_hi = __expf(m_hi - mn_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    l_lo *= c_lo;
+    l_hi *= c_hi;
+    uint32_t pf[4][2], pr[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float p0, p1, p2, p3;
+      if (sig) {
+        p0 = s[j][0], p1 = s[j][1], p2 = s[j][2], p3 = s[j][3];
+      } else {
+        p0 = __expf(s[j][0] - mn_lo), p1 = __expf(s[j][1] - mn_lo), p2 = __expf(s[j][2] - mn_hi), p3 = __expf(s[j][3] - mn_hi);
+      }
+      l_lo += p0 + p1;
+      l_hi += p2 + p3;
+      pf[j][0] = pack_bf16(p0, p1);
+      pf[j][1] = pack_bf16(p2, p3);
+      if (split_p) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pf[j][0]));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pf[j][1]));
+        pr[j][0] = pack_bf16(p0 - a.x, p1 - a.y);
+        pr[j][1] = pack_bf16(p2 - b.x, p3 - b.y);
+      }
+    }
+    if (c_lo != 1.0f || c_hi != 1.0f) {
+#pragma unroll
+      for (int j = 0; j < 2 * DV16M; ++j) {
+        o[j][0] *= c_lo;
+        o[j][1] *= c_lo;
+        o[j][2] *= c_hi;
+        o[j][3] *= c_hi;
+      }
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      const uint32_t af[4] = {pf[2 * ks][0], pf[2 * ks][1], pf[2 * ks + 1][0], pf[2 * ks + 1][1]};
+      const uint32_t ar[4] = {pr[2 * ks][0], pr[2 * ks][1], pr[2 * ks + 1][0], pr[2 * ks + 1][1]};
+#pragma unroll
+      for (int jd = 0; jd < DV16M; ++jd) {
+        if (jd * 16 < Dv) {
+          uint32_t bf[4];
+          const int mi = lane >> 3;
+          ldmatrix_x4_trans(bf, smem_u32(Vt + (16 * ks + (mi & 1) * 8 + (lane & 7)) * ldv + jd * 16 + (mi >> 1) * 8));
+          mma_bf16_16816(o[2 * jd], af, bf[0], bf[1]);
+          mma_bf16_16816(o[2 * jd + 1], af, bf[2], bf[3]);
+          if (split_p) {
+            mma_bf16_16816(o[2 * jd], ar, bf[0], bf[1]);
+            mma_bf16_16816(o[2 * jd + 1], ar, bf[2], bf[3]);
+          }
+        }
+      }
+    }
+    __syncwarp();  // every lane has read the tile before the next one is copied over it
+  }
+  griddep_launch();
+  // ---- merge the warps: each leaves (m, l, O) in its own buffer ([16][Dv] fp32 fits where its 32 key + value rows were)
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  float* Os = reinterpret_cast<float*>(Kt);
+#pragma unroll
+  for (int j = 0; j < 2 * DV16M; ++j) {
+    const int d = 8 * j + 2 * (lane & 3);
+    if (d < Dv) {
+      Os[r_lo * Dv + d] = o[j][0];
+      Os[r_lo * Dv + d + 1] = o[j][1];
+      Os[(r_lo + 8) * Dv + d] = o[j][2];
+      Os[(r_lo + 8) * Dv + d + 1] = o[j][3];
+    }
+  }
+  if ((lane & 3) == 0) {
+    ml[(warp * 16 + r_lo) * 2] = m_lo;
+    ml[(warp * 16 + r_lo) * 2 + 1] = l_lo;
+    ml[(warp * 16 + r_lo + 8) * 2] = m_hi;
+    ml[(warp * 16 + r_lo + 8) * 2 + 1] = l_hi;
+  }
+  __syncthreads();
+  const float* O0 = reinterpret_cast<const float*>(Qs + 16 * ldk);
+  const size_t wstride = (size_t)wbuf / 2;  // floats between two warps' buffers
+  for (int i = threadIdx.x; i < nrow * Dv; i += DT_WARPS * 32) {
+    const int r = i / Dv, d = i - r * Dv;
+    float mt = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DT_WARPS; ++w) mt = fmaxf(mt, ml[(w * 16 + r) * 2]);
+    float lt = 0.f, v = 0.f;
+#pragma unroll
+    for (int w = 0; w < DT_WARPS; ++w) {
+      const float f = mt == -INFINITY ? 0.f : expf(ml[(w * 16 + r) * 2] - mt);  // a warp or a split without keys: m = -inf, l = 0, O = 0
+      lt += ml[(w * 16 + r) * 2 + 1] * f;
+      v += O0[w * wstride + r * Dv + d] * f;
+    }
+    const int64_t row = (int64_t)t * H + h0 + r;
+    if (splits > 1) {
+      float* pp = part + (row * splits + split) * (Dv + 2);
+      if (d == 0) pp[0] = mt, pp[1] = lt;
+      pp[2 + d] = v;
+      continue;
+    }
+    const float res = sig ? v : v / lt;
+    if (out_f32) reinterpret_cast<float*>(out)[row * Dv + d] = res;
+    else reinterpret_cast<__nv_bfloat16*>(out)[row * Dv + d] = __float2bfloat16_rn(res);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -298,6 +521,43 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
   else if (Dv <= 128) PF_LAUNCH(8);
   else PF_LAUNCH(16);
 #undef PF_LAUNCH
+  return B200_OK;
+}
+
+int b200_swa_sink_attn_decode_tc(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                                 int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
+                                 int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
+                                 float softcap, const float* sigmoid_bias, int v_div, int out_f32, int split_p, int splits,
+                                 float* split_workspace, void* stream) {
+  B200_REQUIRE(q && k_pool && v_pool && block_table && tok_row && tok_pos && out, "swa_sink_attn_decode_tc: null pointer");
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && window >= 1 && chunk >= 0, "swa_sink_attn_decode_tc: %d query heads over %d kv heads", H, G);
+  B200_REQUIRE(v_div >= 1 && G % v_div == 0 && !(sigmoid_bias && sink), "swa_sink_attn_decode_tc: %d key heads sharing values by %d", G, v_div);
+  B200_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || split_workspace), "swa_sink_attn_decode_tc: %d key splits need a workspace", splits);
+  if (D % 16 || Dv % 16 || Dv > 256 || D > 512 || v_pitch % 8 || v_pitch < Dv || (ldq & 1) || ((uintptr_t)q & 7) || v_pool == k_pool) {
+    set_last_error("swa_sink_attn_decode_tc: head sizes %d / %d need multiples of 16 (<= 512 / 256) and a value pool of its own", D, Dv);
+    return B200_ERR_UNSUPPORTED;
+  }
+  if (T <= 0) return B200_OK;
+  const int rep = H / G;
+  dim3 grid((unsigned)(T * G * ((rep + 15) / 16)), (unsigned)splits);
+  const size_t smem = ((size_t)16 * (D + 8) + (size_t)DT_WARPS * LDT_KEYS * (D + 8 + Dv + 8)) * 2 + (size_t)DT_WARPS * 16 * 2 * 4;
+  cudaStream_t st = (cudaStream_t)stream;
+  typedef __nv_bfloat16 BT;
+#define DT_LAUNCH(M)                                                                                                            \
+  do {                                                                                                                          \
+    if (smem > 48 * 1024)                                                                                                       \
+      B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_decode_tc_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    B200_CUDA_OK(launch_kernel(swa_sink_decode_tc_kernel<M>, grid, dim3(DT_WARPS * 32), smem, st, q, ldq, (const BT*)k_pool,    \
+                               (const BT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, window, out, H, G, D,  \
+                               Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p,                  \
+                               split_workspace));                                                                               \
+  } while (0)
+  if (Dv <= 64) DT_LAUNCH(4);
+  else if (Dv <= 128) DT_LAUNCH(8);
+  else DT_LAUNCH(16);
+#undef DT_LAUNCH
+  if (splits > 1)
+    return b200_attn_split_merge(split_workspace, splits, Dv, sigmoid_bias ? 1 : 0, out_f32, B200_BF16, out, (int64_t)T * H, stream);
   return B200_OK;
 }
 

@@ -526,6 +526,7 @@ class StepMeta:
     tok_pos: torch.Tensor
     slot_mapping: torch.Tensor  # int64 [T]: KV slot = block id * block_size + offset
     max_new: int = 0            # longest portion of the step (host)
+    max_end: int = 0            # most tokens any sequence of the step holds once the step is done (host)
     # long portions cut into segments the selective scan runs in parallel: int32 [num_segs, 4] = (first token, end token,
     # sequence, 1 = first of its sequence | 2 = last) and int32 [num_seqs + 1] first segment per sequence; None when no
     # portion of the step is long enough
@@ -565,7 +566,8 @@ class StepMeta:
         for a in parts:
             cut.append(dev[o:o + a.size])
             o += a.size
-        meta = StepMeta(b, t, *cut, dev[i32.size:i32.size + 2 * t].view(torch.int64), int(n.max()) if b else 0)
+        meta = StepMeta(b, t, *cut, dev[i32.size:i32.size + 2 * t].view(torch.int64), int(n.max()) if b else 0,
+                        int((pos0 + n).max()) if b else 0)
         seg = ops.SCAN_SEGMENT
         if meta.max_new >= 2 * seg:
             per = np.maximum(1, -(-n // seg))

@@ -780,11 +780,26 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
                                                        block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos), float(scale),
                                                        _ptr(out), t, num_heads, d, dv, bs, _stream()), "b200_latent_attn_decode")
         return out
+    # long contexts at small batch: several CTAs share a (token, kv head)'s keys, so that every SM has its CTAs
+    span = min(getattr(meta, "max_end", 0) or 0, int(window), int(chunk) if chunk else 1 << 30)
+    tc = (k_pool.dtype == torch.bfloat16 and not latent_values and d % 16 == 0 and dv % 16 == 0 and d <= 512 and dv <= 256
+          and q_src.stride(0) % 2 == 0)
+    ctas = t * g * (-(-(num_heads // g) // 16) if tc else 1)
+    splits = max(1, min(8, (148 * (3 if tc else 4)) // max(1, ctas), -(-span // (128 if tc else 512))))
+    ws = torch.empty((t * num_heads * splits * (dv + 2),), dtype=torch.float32, device=q_src.device) if splits > 1 else None
+    if tc:  # decode-sized steps on bf16 pools: the query heads of a kv head are the rows of a tensor-core tile
+        with _k("swa_sink_attn_decode_tc" + tag):
+            check(_cabi.load().b200_swa_sink_attn_decode_tc(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                                            block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos), _ptr(sink),
+                                                            float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, v_pitch, bs,
+                                                            *variant, 1 if split_p else 0, splits, _ptr(ws), _stream()),
+                  "b200_swa_sink_attn_decode_tc")
+        return out
     with _k("swa_sink_attn" + tag):
         check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
                                               _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
                                               _ptr(sink), float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, v_pitch, bs,
-                                              *variant, _stream()), "b200_swa_sink_attn")
+                                              *variant, splits, _ptr(ws), _stream()), "b200_swa_sink_attn")
     return out
 
 
