@@ -267,6 +267,7 @@ __global__ void __launch_bounds__(128, DV16M <= 8 ? 4 : 2)
 // shared memory.  gridDim.y CTAs may split the keys further; their partial results go to `part` (attn_split_merge_kernel).
 // Same variants as the kernels above.
 constexpr int DT_WARPS = 4;
+constexpr int DT_SLOTS = 3;  // 16-byte chunks per lane and tile row: (512 key + 256 value columns) / 8 / 32
 
 template <int DV16M>
 __global__ void __launch_bounds__(DT_WARPS * 32)
@@ -280,23 +281,27 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   extern __shared__ __align__(16) unsigned char dt_sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.y, splits = gridDim.y;
-  const int rep = H / G, hbn = (rep + 15) / 16;
-  const int hb = blockIdx.x % hbn, g = (blockIdx.x / hbn) % G, t = blockIdx.x / (hbn * G);
-  const int h0 = g * rep + hb * 16, nrow = rep - hb * 16 < 16 ? rep - hb * 16 : 16;  // this CTA's heads h0 .. h0 + nrow
-  const int Gv = G / v_div, gv = g / v_div;
+  // The v_div key heads that share a value head (several score maps over the same values) are served by ONE CTA: a key row of
+  // the tile is their rows side by side (width v_div * D) and a query row is zero outside its own key head's columns, so the
+  // values are fetched once for all maps.  rep = query heads per VALUE head; they are consecutive heads.
+  const int Gv = G / v_div, rep = H / Gv, hbn = (rep + 15) / 16, per_key = H / G;
+  const int hb = blockIdx.x % hbn, gv = (blockIdx.x / hbn) % Gv, t = blockIdx.x / (hbn * Gv);
+  const int h0 = gv * rep + hb * 16, nrow = rep - hb * 16 < 16 ? rep - hb * 16 : 16;  // this CTA's heads h0 .. h0 + nrow
+  const int Dk = v_div * D;
   const bool sig = sig_bias != nullptr;
   const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
-  const int ldk = D + 8, ldv = Dv + 8, wbuf = LDT_KEYS * (ldk + ldv);
+  const int ldk = Dk + 8, ldv = Dv + 8, wbuf = LDT_KEYS * (ldk + ldv);
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(dt_sm);             // [16][ldk]
   __nv_bfloat16* Kt = Qs + 16 * ldk + (size_t)warp * wbuf;                  // this warp's [32][ldk] keys, then [32][ldv] values
   __nv_bfloat16* Vt = Kt + LDT_KEYS * ldk;
   float* ml = reinterpret_cast<float*>(Qs + 16 * ldk + (size_t)DT_WARPS * wbuf);  // [warps][16][2]
   const int pos = tok_pos[t];
   const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
-  for (int i = threadIdx.x; i < 16 * (D / 2); i += DT_WARPS * 32) {
-    const int r = i / (D / 2), d = (i - r * (D / 2)) * 2;
+  for (int i = threadIdx.x; i < 16 * (Dk / 2); i += DT_WARPS * 32) {
+    const int r = i / (Dk / 2), d = (i - r * (Dk / 2)) * 2;
+    const int mine = (hb * 16 + r) / per_key;  // which of the CTA's key heads row r belongs to
     float2 v = make_float2(0.f, 0.f);
-    if (r < nrow) v = *reinterpret_cast<const float2*>(q + (int64_t)t * ldq + (int64_t)(h0 + r) * D + d);
+    if (r < nrow && d / D == mine) v = *reinterpret_cast<const float2*>(q + (int64_t)t * ldq + (int64_t)(h0 + r) * D + (d - mine * D));
     *reinterpret_cast<__nv_bfloat162*>(Qs + r * ldk + d) = __floats2bfloat162_rn(v.x, v.y);
   }
   __syncthreads();
@@ -314,22 +319,44 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   for (int j = 0; j < 2 * DV16M; ++j)
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[j][c] = 0.f;
-  const int kch = D / 8, vch = Dv / 8;  // 16-byte chunks per row
+  const int kch = D / 8, kcht = v_div * kch, vch = Dv / 8;  // 16-byte chunks per key head's row, per tile row, per value row
+  // the 16-byte chunks of a tile row that this lane copies (the same for every row and tile): key chunk c of key head mp comes
+  // from that head's row, bs rows after the first head's
+  bool ch_on[DT_SLOTS];
+  int ch_heads[DT_SLOTS], ch_head[DT_SLOTS], ch_rowlen[DT_SLOTS], ch_src[DT_SLOTS], ch_pitch[DT_SLOTS];
+  uint32_t ch_dst[DT_SLOTS];
+  const __nv_bfloat16* ch_pool[DT_SLOTS];
+#pragma unroll
+  for (int sl = 0; sl < DT_SLOTS; ++sl) {
+    const int c = lane + 32 * sl;
+    const bool key = c < kcht;
+    const int mp = key ? c / kch : 0;
+    ch_on[sl] = c < kcht + vch;
+    ch_heads[sl] = key ? G : Gv;
+    ch_head[sl] = key ? gv * v_div : gv;
+    ch_rowlen[sl] = key ? D : v_pitch;
+    ch_pool[sl] = key ? k_pool : v_pool;
+    ch_src[sl] = key ? mp * bs * D + (c - mp * kch) * 8 : (c - kcht) * 8;
+    ch_pitch[sl] = (key ? ldk : ldv) * 2;
+    ch_dst[sl] = key ? smem_u32(Kt) + c * 16 : smem_u32(Vt) + (c - kcht) * 16;
+  }
   for (int j0 = lo + LDT_KEYS * (warp + DT_WARPS * split); j0 <= pos; j0 += LDT_KEYS * DT_WARPS * splits) {
     // ---- this warp's 32 key and value rows -> its buffer (rows past the token's position are zeros)
     const int jm = j0 + lane;
-    int64_t my_k = -1, my_v = -1;
+    int my_blk = -1, my_off = 0;
     if (jm <= pos) {
-      const int64_t blk = bt[jm / bs];
-      my_k = (blk * G + g) * bs + (jm % bs);
-      my_v = (blk * Gv + gv) * bs + (jm % bs);
+      my_blk = bt[jm / bs];
+      my_off = jm % bs;
     }
     for (int r = 0; r < LDT_KEYS; ++r) {
-      const int64_t kr = __shfl_sync(0xffffffffu, my_k, r), vr = __shfl_sync(0xffffffffu, my_v, r);
-      const bool ok = kr >= 0;
-      for (int c = lane; c < kch + vch; c += 32) {
-        if (c < kch) cp_async16(smem_u32(Kt + r * ldk + c * 8), k_pool + (ok ? kr : 0) * D + c * 8, ok);
-        else cp_async16(smem_u32(Vt + r * ldv + (c - kch) * 8), v_pool + (ok ? vr : 0) * v_pitch + (c - kch) * 8, ok);
+      const int blk = __shfl_sync(0xffffffffu, my_blk, r), off = __shfl_sync(0xffffffffu, my_off, r);
+      const bool ok = blk >= 0;
+#pragma unroll
+      for (int sl = 0; sl < DT_SLOTS; ++sl) {
+        if (ch_on[sl]) {
+          const int64_t row = ((int64_t)(ok ? blk : 0) * ch_heads[sl] + ch_head[sl]) * bs + off;
+          cp_async16(ch_dst[sl] + r * ch_pitch[sl], ch_pool[sl] + row * ch_rowlen[sl] + ch_src[sl], ok);
+        }
       }
     }
     cp_async_commit();
@@ -342,7 +369,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
 #pragma unroll
       for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
 #pragma unroll 2
-    for (int kk = 0; kk < D; kk += 16) {
+    for (int kk = 0; kk < Dk; kk += 16) {
       uint32_t af[4];
       ldmatrix_x4(af, smem_u32(Qs + (lane & 15) * ldk + kk + (lane >> 4) * 8));
 #pragma unroll
@@ -538,9 +565,13 @@ int b200_swa_sink_attn_decode_tc(const float* q, int ldq, const void* k_pool, co
     return B200_ERR_UNSUPPORTED;
   }
   if (T <= 0) return B200_OK;
-  const int rep = H / G;
-  dim3 grid((unsigned)(T * G * ((rep + 15) / 16)), (unsigned)splits);
-  const size_t smem = ((size_t)16 * (D + 8) + (size_t)DT_WARPS * LDT_KEYS * (D + 8 + Dv + 8)) * 2 + (size_t)DT_WARPS * 16 * 2 * 4;
+  const int Gv = G / v_div, rep = H / Gv, Dk = v_div * D;  // query heads per value head; width of a tile's key rows
+  if (Dk > 512) {
+    set_last_error("swa_sink_attn_decode_tc: %d key heads of %d side by side exceed 512 columns", v_div, D);
+    return B200_ERR_UNSUPPORTED;
+  }
+  dim3 grid((unsigned)(T * Gv * ((rep + 15) / 16)), (unsigned)splits);
+  const size_t smem = ((size_t)16 * (Dk + 8) + (size_t)DT_WARPS * LDT_KEYS * (Dk + 8 + Dv + 8)) * 2 + (size_t)DT_WARPS * 16 * 2 * 4;
   cudaStream_t st = (cudaStream_t)stream;
   typedef __nv_bfloat16 BT;
 #define DT_LAUNCH(M)                                                                                                            \

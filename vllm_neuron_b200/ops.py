@@ -782,9 +782,10 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
         return out
     # long contexts at small batch: several CTAs share a (token, kv head)'s keys, so that every SM has its CTAs
     span = min(getattr(meta, "max_end", 0) or 0, int(window), int(chunk) if chunk else 1 << 30)
-    tc = (k_pool.dtype == torch.bfloat16 and not latent_values and d % 16 == 0 and dv % 16 == 0 and d <= 512 and dv <= 256
+    tc = (k_pool.dtype == torch.bfloat16 and not latent_values and d % 16 == 0 and dv % 16 == 0 and d * v_div <= 512 and dv <= 256
           and q_src.stride(0) % 2 == 0)
-    ctas = t * g * (-(-(num_heads // g) // 16) if tc else 1)
+    gv = g // v_div
+    ctas = t * gv * -(-(num_heads // gv) // 16) if tc else t * g
     splits = max(1, min(8, (148 * (3 if tc else 4)) // max(1, ctas), -(-span // (128 if tc else 512))))
     ws = torch.empty((t * num_heads * splits * (dv + 2),), dtype=torch.float32, device=q_src.device) if splits > 1 else None
     if tc:  # decode-sized steps on bf16 pools: the query heads of a kv head are the rows of a tensor-core tile
