@@ -322,8 +322,9 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   const int kch = D / 8, kcht = v_div * kch, vch = Dv / 8;  // 16-byte chunks per key head's row, per tile row, per value row
   // the 16-byte chunks of a tile row that this lane copies (the same for every row and tile): key chunk c of key head mp comes
   // from that head's row, bs rows after the first head's
+  // source offset of a chunk = block * ch_blk + (row of the block) * ch_row + ch_src elements into ch_pool
   bool ch_on[DT_SLOTS];
-  int ch_heads[DT_SLOTS], ch_head[DT_SLOTS], ch_rowlen[DT_SLOTS], ch_src[DT_SLOTS], ch_pitch[DT_SLOTS];
+  int ch_blk[DT_SLOTS], ch_row[DT_SLOTS], ch_src[DT_SLOTS], ch_pitch[DT_SLOTS];
   uint32_t ch_dst[DT_SLOTS];
   const __nv_bfloat16* ch_pool[DT_SLOTS];
 #pragma unroll
@@ -332,11 +333,10 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     const bool key = c < kcht;
     const int mp = key ? c / kch : 0;
     ch_on[sl] = c < kcht + vch;
-    ch_heads[sl] = key ? G : Gv;
-    ch_head[sl] = key ? gv * v_div : gv;
-    ch_rowlen[sl] = key ? D : v_pitch;
+    ch_row[sl] = key ? D : v_pitch;
+    ch_blk[sl] = (key ? G : Gv) * bs * ch_row[sl];
     ch_pool[sl] = key ? k_pool : v_pool;
-    ch_src[sl] = key ? mp * bs * D + (c - mp * kch) * 8 : (c - kcht) * 8;
+    ch_src[sl] = key ? (gv * v_div + mp) * bs * D + (c - mp * kch) * 8 : gv * bs * v_pitch + (c - kcht) * 8;
     ch_pitch[sl] = (key ? ldk : ldv) * 2;
     ch_dst[sl] = key ? smem_u32(Kt) + c * 16 : smem_u32(Vt) + (c - kcht) * 16;
   }
@@ -353,10 +353,9 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       const bool ok = blk >= 0;
 #pragma unroll
       for (int sl = 0; sl < DT_SLOTS; ++sl) {
-        if (ch_on[sl]) {
-          const int64_t row = ((int64_t)(ok ? blk : 0) * ch_heads[sl] + ch_head[sl]) * bs + off;
-          cp_async16(ch_dst[sl] + r * ch_pitch[sl], ch_pool[sl] + row * ch_rowlen[sl] + ch_src[sl], ok);
-        }
+        if (ch_on[sl])
+          cp_async16(ch_dst[sl] + r * ch_pitch[sl],
+                     ch_pool[sl] + ((int64_t)(ok ? blk : 0) * ch_blk[sl] + (off * ch_row[sl] + ch_src[sl])), ok);
       }
     }
     cp_async_commit();
