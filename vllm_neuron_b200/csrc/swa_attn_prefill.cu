@@ -2,7 +2,7 @@
 // swa_attn.cu -- a query at position i attends keys i - window < j <= i through its block table, the softmax starts
 // from the per-head sink (running maximum = sink, denominator = 1, no value; none when sink == NULL) -- computed
 // FlashAttention-style.  Value rows have pitch v_pitch (the value pool may alias the leading columns of the key pool).
-//   CTA = 64 consecutive new tokens of one sequence x one query head, 4 warps x 16 rows.  Keys are walked in tiles of 32
+//   CTA = PF_ROWS (64) consecutive new tokens of one sequence x one query head, a warp per 16 rows.  Keys are walked in tiles of 32
 //   from the first key the tile's first row may see to the last key its last row may see; each tile's K and V rows are
 //   gathered page by page into shared memory with cp.async, one tile ahead of the MMAs (rows padded by 16 bytes:
 //   conflict-free ldmatrix), S = Q K^T and O += P V run
@@ -19,6 +19,7 @@
 namespace b200 {
 
 constexpr int PF_ROWS = 64;
+constexpr int PF_THREADS = PF_ROWS * 2;  // a warp per 16 query rows
 constexpr int PF_KEYS = 32;
 constexpr int PF_NT = PF_KEYS / 8;  // n8 score tiles per key tile
 constexpr int LDT_KEYS = 32;  // keys per warp tile of the decode-sized kernel
@@ -26,7 +27,7 @@ constexpr int PF_STAGES = 2;  // ring of K / V tiles: the next tile's cp.async c
                               // stage costs a resident CTA per SM and measured slower)
 
 template <int DV16M>  // accumulator capacity: Dv <= 16 * DV16M
-__global__ void __launch_bounds__(128, DV16M <= 8 ? 4 : 2)
+__global__ void __launch_bounds__(PF_THREADS, DV16M <= 8 ? 512 / PF_THREADS : 256 / PF_THREADS)
     swa_sink_prefill_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
                             const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
@@ -54,7 +55,7 @@ __global__ void __launch_bounds__(128, DV16M <= 8 ? 4 : 2)
   const int pos0 = seq_pos0[sq];
   const int32_t* bt = block_table + (int64_t)seq_slot[sq] * bt_stride;
   // ---- Q tile: fp32 rows -> bf16 shared memory (rows past the portion are zero)
-  for (int i = tid; i < PF_ROWS * (D / 2); i += 128) {
+  for (int i = tid; i < PF_ROWS * (D / 2); i += PF_THREADS) {
     const int r = i / (D / 2), d = (i - r * (D / 2)) * 2;
     float2 v = make_float2(0.f, 0.f);
     if (i0 + r < n) v = *reinterpret_cast<const float2*>(q + (int64_t)(t0 + i0 + r) * ldq + (int64_t)h * D + d);
@@ -87,7 +88,7 @@ __global__ void __launch_bounds__(128, DV16M <= 8 ? 4 : 2)
   const int kch = D / 8, vch = v_alias ? 0 : Dv / 8;  // 16-byte chunks per row
   // one tile of 32 keys (K and V rows, page by page through the block table) into stage `st`; rows past j_hi are zeros.
   // Four threads share a row and take its 16-byte chunks in turn, so the page look-up happens once per thread and tile.
-  constexpr int TPR = 128 / PF_KEYS;
+  constexpr int TPR = PF_THREADS / PF_KEYS;
   const int ir = tid / TPR, ic = tid % TPR;
   // the page of this thread's row in the tile at j0 (looked up one tile before the copies that need it are issued)
   auto page_of = [&](int j0) -> int64_t {
@@ -539,7 +540,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
   do {                                                                                                                        \
     if (smem > 48 * 1024)                                                                                                     \
       B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_prefill_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    B200_CUDA_OK(launch_kernel(swa_sink_prefill_kernel<M>, grid, dim3(128), smem, st, q, ldq, (const BT*)k_pool,              \
+    B200_CUDA_OK(launch_kernel(swa_sink_prefill_kernel<M>, grid, dim3(PF_THREADS), smem, st, q, ldq, (const BT*)k_pool,              \
                                (const BT*)v_pool, block_table, bt_stride, seq_start, seq_slot, seq_pos0, sink, scale, window, \
                                out, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p, bs_shift)); \
   } while (0)
