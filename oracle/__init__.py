@@ -11,7 +11,7 @@ Parity status
   the reference's Python (file:line cited per function) and are checked against
   golden vectors produced by importing the reference's own modules in the
   authoring container (``tests/golden/gen_from_reference.py``).
-* Arithmetic side (``kv_ref``, ``attn_ref``, ``quant_ref``, ``llama_ref``): PINNED TO HF TRANSFORMERS (round 2).
+* Arithmetic side (``kv_ref``, ``attn_ref``, ``quant_ref``, ``llama_ref``): PINNED TO HF TRANSFORMERS.
   The reference delegates every floating-point op to neuronx-distributed-inference (NxDI, AWS Neuron SDK 2.26.1),
   which is neither vendored under /root/reference nor installable here, and no reference test pins a numeric
   attention/GEMM/KV result; the reference's own accuracy method is greedy generation with HF transformers on CPU

@@ -80,7 +80,7 @@ def _oracle_check(res, quant, band, widen_once=False):
 
 # Committed floors on the number of engine tokens that ARE the oracle's argmax (the rest must sit inside the error band).
 # Two or three below the lowest count ever measured: room for a near-tie flipping with the CPU oracle's thread count,
-# none for a real regression (VERDICT round 2, weak item 1).
+# none for a real regression.
 EXACT_FLOOR = {"bf16": 102, "fp8": 82, "native": 101, "cfg1": 236, "tp2": 101}
 
 

@@ -47,6 +47,20 @@ def cfg_b():
     ]}
 
 
+def cfg_c():
+    """Tensor-core sizes throughout, but three gated heads: the joint projection has an ODD number of rows (its fp32 output rows
+    start at odd offsets), three query heads share one kv head, and the two maps of a head are wider than its values."""
+    return {"architecture": "Zudarax", "vocab": 128, "width": 128, "norm": {"eps": 1e-6, "groups": 8}, "layers": [
+        _layer("attention_2", 64, heads=3, kv_heads=1, dim=32, vdim=16, diff=0.25, scale=0.18, rot=_rot(32, 10000.0)),
+        _layer("attention", 48, heads=3, kv_heads=3, dim=16, vdim=32, conv=2, scale=0.25, softcap=6.0, mask={"size": 40},
+               rot=_rot(8, 1000.0)),
+        _layer("attention_2", None, heads=6, kv_heads=3, dim=16, vdim=48, diff=0.7, scale=0.25, rot=_rot(16, 500.0)),
+        # optional entries left out: no convolution (the biases still count), no cap, no chunks; no convolution before the sigmoid
+        _layer("attention", 32, heads=2, kv_heads=1, dim=32, vdim=32, scale=0.2, rot=_rot(16, 100.0)),
+        _layer("attention_3", 32, heads=2, kv_heads=2, dim=16, vdim=16, scale=0.3, rot=_rot(16, 100.0)),
+    ]}
+
+
 class Case:
     def __init__(self, cfgd, dtype, seed=0, max_num_seqs=3, pool_tokens=1024):
         from vllm_neuron_b200.engine import B200Engine
@@ -112,7 +126,7 @@ def _portions(n, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("cfg", [cfg_a, cfg_b])
+@pytest.mark.parametrize("cfg", [cfg_a, cfg_b, cfg_c])
 def test_whole_prompt_decode_and_portions_agree_with_the_restatement(cfg, dtype):
     c = Case(cfg(), dtype)
     toks = c.tokens(150, 1)
