@@ -363,6 +363,17 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
                                int Dv, int v_pitch, int block_size, int chunk, float softcap, const float* sigmoid_bias, int v_div,
                                int out_f32, int split_p, void* stream);
+/* Prompt portions on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory): same ragged step arguments as
+ * b200_swa_sink_attn_prefill, no sink and no window.  Kernels exist for pages of 32 tokens and D = Dv = 64 or 128 (softmax,
+ * capped softmax, sigmoid weights) and, with v_div = 2, D = 64 with Dv = 64 or 128 (softmax); q rows must be 16-byte aligned.
+ * b200_swa_sink_attn_prefill_tc_supported says whether a combination has one; the launch returns B200_ERR_UNSUPPORTED
+ * otherwise.  num_blocks = pages of the pools. */
+int b200_swa_sink_attn_prefill_tc_supported(int D, int Dv, int block_size, int v_div, int capped, int sigmoid);
+int b200_swa_sink_attn_prefill_tc(const float* q, int ldq, const void* k_pool, const void* v_pool, int num_blocks,
+                                  const int32_t* block_table, int64_t bt_stride, const int32_t* seq_start,
+                                  const int32_t* seq_slot, const int32_t* seq_pos0, int B, int max_new, float scale, void* out,
+                                  int H, int G, int D, int Dv, int block_size, int chunk, float softcap,
+                                  const float* sigmoid_bias, int v_div, int out_f32, int split_p, void* stream);
 /* The same attention for decode-sized steps on the tensor cores (bf16 pools with a value pool of its own; D and Dv multiples of
  * 16, Dv <= 256, else B200_ERR_UNSUPPORTED): the query heads of a kv head are the rows of one MMA tile, each key and value row
  * is fetched once for all of them.  Arguments as b200_swa_sink_attn (+ split_p as in the prompt kernel). */

@@ -298,3 +298,97 @@ def test_two_score_maps_over_shared_values_in_fp32(kv_dtype):
     if kv_dtype == torch.bfloat16:                                            # one bf16 term alone is visibly coarser
         coarse = _attend(q, k, v, scale, kv_dtype=kv_dtype, portions=[T], out_f32=True, split_p=False)
         assert 1e-4 < _err(coarse, want) < 6e-3
+
+
+# ------------------------------------------------------------------------------------------------ long prompt portions (tcgen05 kernel)
+def _attend_steps(seqs, steps, scale, *, bs=32, **variant):
+    """Several sequences through bf16 pools of 32-token pages.  seqs: name -> (q [T, H, D], k [T, G, D], v [T, Gv, P]); steps:
+    lists of (name, n), all entries of a step in one launch.  Pages are dealt out in an interleaved, descending order.
+    -> name -> [T, H, P], and the names of the kernels that ran."""
+    ops = _ops()
+    names = list(seqs)
+    q0, k0, v0 = seqs[names[0]]
+    H, D, G, Gv, P = q0.shape[1], q0.shape[2], k0.shape[1], v0.shape[1], v0.shape[2]
+    need = {s: -(-seqs[s][0].shape[0] // bs) for s in names}
+    nb = sum(need.values()) + 1
+    free = list(range(nb - 1, 0, -1))
+    pages = {i + 1: [] for i in range(len(names))}
+    for r in range(max(need.values())):
+        for i, s in enumerate(names):
+            if r < need[s]:
+                pages[i + 1].append(free.pop(0))
+    k_pool = torch.zeros(nb, G, bs, D, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.zeros(nb, Gv, bs, P, dtype=torch.bfloat16, device=DEV)
+    table = torch.zeros(len(names) + 1, max(need.values()) + 1, dtype=torch.int32, device=DEV)
+    for r, pg in pages.items():
+        table[r, :len(pg)] = torch.tensor(pg, dtype=torch.int32)
+    at = {s: 0 for s in names}
+    out = {s: [] for s in names}
+    with ops.kernel_timer() as timer:
+        for step in steps:
+            entries = [(names.index(s) + 1, at[s], n) for s, n in step]
+            meta = _meta(entries, pages, bs)
+            rows = torch.cat([torch.cat([t[at[s]:at[s] + n].reshape(n, -1) for t in seqs[s]], dim=1) for s, n in step]).to(DEV)
+            qd = ops.qk_norm_rope_kv_write(rows, 0, H * D, (H + G) * D, H, k_pool, v_pool, meta)
+            a = ops.swa_sink_attn(qd, H, k_pool, v_pool, table, meta, None, scale, NO_WINDOW, **variant).float()
+            o = 0
+            for s, n in step:
+                out[s].append(a[o:o + n].view(n, H, P))
+                o, at[s] = o + n, at[s] + n
+    assert all(at[s] == seqs[s][0].shape[0] for s in names)
+    return {s: torch.cat(v) for s, v in out.items()}, set(timer.summary())
+
+
+TC_CASES = {
+    # name: (H, G, Gv, D, P, variant)
+    "softmax 128": (4, 2, 2, 128, 128, {}),
+    "softmax 64, odd group": (3, 1, 1, 64, 64, {}),
+    "capped chunks of 200": (4, 2, 2, 128, 128, {"chunk": 200, "softcap": 3.0}),
+    "capped chunks of 128": (2, 2, 2, 64, 64, {"chunk": 128, "softcap": 5.0}),
+    "chunks of 48": (4, 1, 1, 64, 64, {"chunk": 48}),
+    "sigmoid 128": (4, 2, 2, 128, 128, {"sigmoid": True}),
+    "sigmoid 64": (2, 1, 1, 64, 64, {"sigmoid": True}),
+    "two maps, values of 128": (8, 4, 2, 64, 128, {"out_f32": True}),
+    "two maps, values of 64": (12, 4, 2, 64, 64, {"out_f32": True}),
+}
+
+
+@pytest.mark.parametrize("case", list(TC_CASES))
+def test_long_prompt_portions_on_the_tcgen05_kernel(case):
+    """Portions of 128 tokens and more take the tcgen05 kernel.  Three sequences of unequal length in ragged steps (a long
+    portion beside single tokens and short portions, cuts inside pages, key steps and chunks), keys made loud on both sides of
+    every chunk border and one far key that wins late, against the restatement; the kernel must really have run."""
+    from oracle.zudarax_ref import sigmoid_attention, softmax_attention, visible
+
+    H, G, Gv, D, P, variant = TC_CASES[case]
+    variant = dict(variant)
+    g = torch.Generator().manual_seed(len(case))
+    scale, chunk, cap = 0.5 * D ** -0.5, variant.get("chunk", 0), variant.get("softcap", 0.0)
+    lens = {"a": 700, "b": 130, "c": 391}
+    seqs, want = {}, {}
+    bias = torch.linspace(-3.0, 1.0, H)
+    for s, T in lens.items():
+        q, k, v = _bf16_values(T, H, D, g=g), _bf16_values(T, G, D, g=g), _bf16_values(T, Gv, P, g=g)
+        if chunk:
+            for j in range(T):
+                if j % chunk in (0, chunk - 1):
+                    k[j] *= 4
+        k[2] = 0
+        k[2, :, 0] = 16.0
+        q[T - 60:, :, 0] = 16.0                                              # key 2 wins for the last queries (where it is visible)
+        k = k.to(torch.bfloat16).float()
+        seqs[s] = (q, k, v)
+        if variant.get("sigmoid"):
+            want[s] = sigmoid_attention(q.double(), k.double(), v.double(), scale, visible(T), bias.double())
+        else:
+            want[s] = softmax_attention(q.double(), k.double(), v.double(), scale, visible(T, chunk) if chunk else visible(T), cap or None)
+    if variant.pop("sigmoid", False):
+        variant["sigmoid_bias"] = bias.to(DEV)
+    steps = [[("a", 300), ("b", 1), ("c", 2)], [("a", 129), ("b", 129)], [("c", 260), ("a", 1)], [("a", 270), ("c", 128)], [("c", 1)]]
+    got, ran = _attend_steps(seqs, steps, scale, split_p=True, **variant)
+    assert any(n.startswith("swa_sink_attn_prefill_tc") for n in ran), ran
+    tol = 2e-4 if variant.get("out_f32") else 6e-3
+    for s in lens:
+        assert _err(got[s], want[s]) < tol, (s, _err(got[s], want[s]))
+    whole, _ = _attend_steps({"a": seqs["a"]}, [[("a", 700)]], scale, split_p=True, **variant)
+    assert _err(whole["a"], want["a"]) < tol

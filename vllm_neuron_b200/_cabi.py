@@ -83,6 +83,9 @@ SIGNATURES = {
                                 _i, _p, _p]),
     "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _f,
                                         _p, _i, _i, _i, _p]),
+    "b200_swa_sink_attn_prefill_tc_supported": (_i, [_i, _i, _i, _i, _i, _i]),
+    "b200_swa_sink_attn_prefill_tc": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _i, _i, _f, _p, _i, _i, _i, _i, _i, _i, _f, _p, _i,
+                                           _i, _i, _p]),
     "b200_swa_sink_attn_decode_tc": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i,
                                           _i, _i, _i, _p, _p]),
     "b200_attn_split_merge": (_i, [_p, _i, _i, _i, _i, _i, _p, _i64, _p]),

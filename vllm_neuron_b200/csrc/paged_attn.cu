@@ -712,6 +712,11 @@ int launch_prefill(const CUtensorMap& km, const CUtensorMap& vm, const void* q, 
 
 }  // namespace
 
+// the cached pool map for the other attention files of the library
+namespace b200 {
+int kv_pool_tmap(const void* pool, int num_blocks, int Hkv, int D, CUtensorMap* out) { return pool_tmap(pool, num_blocks, Hkv, D, out); }
+}  // namespace b200
+
 extern "C" {
 
 size_t b200_paged_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_blocks, int min_quota) {

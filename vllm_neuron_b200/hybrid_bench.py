@@ -85,7 +85,7 @@ def _zudarax_floors(name, t, s_pre, ctx, b, prefill):
     else:
         full, chk, kv_full, kv_chk = ctx + 1, ctx % ck + 1, b * (ctx + 1), b * (ctx % ck + 1)
     out = {}
-    for kern in ("swa_sink_attn_prefill", "swa_sink_attn", "swa_sink_attn_decode_tc"):
+    for kern in ("swa_sink_attn_prefill", "swa_sink_attn_prefill_tc", "swa_sink_attn", "swa_sink_attn_decode_tc"):
         out[kern + "[chunk+cap]"] = att(chk, kv_chk)
         out[kern + "[sigmoid]"] = att(full, kv_full)
         out[kern + "[maps]"] = att(full, kv_full, 2)

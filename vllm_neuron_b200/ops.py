@@ -5,6 +5,8 @@ sm_100a kernels in libb200_paged.so.  Nothing in this file computes on the host.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _cabi
@@ -730,6 +732,8 @@ def kv_write_vmix(qkv, k_col0: int, v_col0: int, k_pool, v_pool, slot_mapping, *
 
 
 PREFILL_ATTN_MIN_TOKENS = 16  # longest portion of a step from which the tensor-core attention kernel is used
+PREFILL_TC_MIN_TOKENS = 128   # ... and from which the tcgen05 kernel with its 128-row query tiles is
+_SWA_PREFILL_LEGACY = bool(os.environ.get("B200_SWA_PREFILL_LEGACY"))
 
 
 def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink, scale: float, window: int,
@@ -760,8 +764,22 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
     # the per-launch timer tells the variants apart (their floors differ)
     tag = "" if plain else "[" + "+".join(n for n, on in (("chunk", chunk), ("cap", softcap), ("sigmoid", sigmoid_bias is not None),
                                                             ("maps", v_div > 1)) if on) + "]"
-    # prompt portions in bf16 serving: the tensor-core kernel; decode-sized steps, fp32 pools and odd head sizes: one CTA per
-    # (token, head) on the CUDA cores
+    # long prompt portions in bf16 serving, head sizes of 64 / 128 with pages of 32 tokens: the tcgen05 kernel (128-row query
+    # tiles, accumulators in tensor memory); B200_SWA_PREFILL_LEGACY=1 keeps the mma.sync kernel (A/B aid)
+    if (k_pool.dtype == torch.bfloat16 and meta.max_new >= PREFILL_TC_MIN_TOKENS and sink is None and window >= (1 << 30)
+            and not latent_values and q_src.stride(0) % 4 == 0 and q_src.data_ptr() % 16 == 0 and not _SWA_PREFILL_LEGACY
+            and _cabi.load().b200_swa_sink_attn_prefill_tc_supported(d, dv, bs, v_div, 1 if softcap else 0,
+                                                                     0 if sigmoid_bias is None else 1)):
+        with _k("swa_sink_attn_prefill_tc" + tag):
+            check(_cabi.load().b200_swa_sink_attn_prefill_tc(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0],
+                                                             _ptr(block_table), block_table.stride(0), _ptr(meta.seq_start),
+                                                             _ptr(meta.seq_slot), _ptr(meta.seq_pos0), meta.num_seqs, meta.max_new,
+                                                             float(scale), _ptr(out), num_heads, g, d, dv, bs, *variant,
+                                                             1 if split_p else 0, _stream()),
+                  "b200_swa_sink_attn_prefill_tc")
+        return out
+    # shorter prompt portions in bf16 serving: the mma.sync kernel; decode-sized steps, fp32 pools and odd head sizes: one CTA
+    # per (token, head) on the CUDA cores
     if (k_pool.dtype == torch.bfloat16 and meta.max_new >= PREFILL_ATTN_MIN_TOKENS and d % 16 == 0 and dv % 16 == 0
             and d <= 512 and dv <= 256 and q_src.stride(0) % 2 == 0):
         with _k("swa_sink_attn_prefill" + tag):
