@@ -61,6 +61,22 @@ def cfg_c():
     ]}
 
 
+def cfg_d():
+    """Head sizes of 64 and 128 throughout: prompt portions of 128 tokens and more run on the tcgen05 attention kernel, shorter
+    ones on the mma.sync kernel, single tokens on the decode kernel -- all three must agree.  A chunk that is no multiple of
+    the 128-key step, an odd number of query heads per kv head, two maps with values as wide as a map and twice as wide."""
+    yarn = {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0}
+    return {"architecture": "Zudarax", "vocab": 160, "width": 128, "norm": {"eps": 1e-6, "groups": 2}, "layers": [
+        _layer("attention_2", 96, heads=2, kv_heads=1, dim=64, vdim=128, diff=0.4, scale=0.125, rot=_rot(16, 10000.0)),
+        _layer("attention", 64, heads=3, kv_heads=1, dim=128, vdim=128, conv=3, scale=0.09, softcap=8.0, mask={"size": 72},
+               rot=_rot(64, 20000.0)),
+        _layer("attention_3", 64, heads=4, kv_heads=2, dim=64, vdim=64, conv=2, scale=0.125, rot=_rot(64, 1000.0, yarn)),
+        _layer("attention_2", None, heads=4, kv_heads=2, dim=64, vdim=64, diff=0.7, scale=0.125, rot=_rot(32, 500.0)),
+        _layer("attention", 64, heads=2, kv_heads=2, dim=64, vdim=64, scale=0.125, rot=_rot(8, 100.0)),
+        _layer("attention_3", None, heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, rot=_rot(32, 250000.0)),
+    ]}
+
+
 class Case:
     def __init__(self, cfgd, dtype, seed=0, max_num_seqs=3, pool_tokens=1024):
         from vllm_neuron_b200.engine import B200Engine
@@ -140,6 +156,24 @@ def test_whole_prompt_decode_and_portions_agree_with_the_restatement(cfg, dtype)
     c.check(cut, {"p": toks})
     d = (cut["p"] - whole["w"]).abs().max().item() / whole["w"].abs().max().item()
     assert d < (1e-5 if dtype == "float32" else 0.05), d                      # how the prompt was cut does not matter
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_short_portions_and_single_tokens_agree(dtype):
+    """A 700-token prompt whole, in portions on both sides of the 128-token switch between the prompt kernels, and beside two
+    other requests (one decoding, one with a long portion of its own) through three rows."""
+    c = Case(cfg_d(), dtype, max_num_seqs=3, pool_tokens=2048)
+    toks, other, short = c.tokens(700, 5), c.tokens(300, 6), c.tokens(40, 7)
+    whole = c.replay({"w": toks}, [[("w", 700)]])
+    c.check(whole, {"w": toks})
+    cut = c.replay({"p": toks}, [[("p", n)] for n in _portions(700, [130, 2, 127, 128, 1, 200, 31, 81])])
+    c.check(cut, {"p": toks})
+    d = (cut["p"] - whole["w"]).abs().max().item() / whole["w"].abs().max().item()
+    assert d < (1e-5 if dtype == "float32" else 0.05), d
+    reqs = {"a": toks, "b": other, "c": short}
+    sched = [[("a", 300), ("c", 1)], [("a", 1), ("b", 129), ("c", 1)], [("a", 270), ("b", 171), ("c", 2)]] + \
+            [[("a", 1), ("c", 1)] for _ in range(36)] + [[("a", 93)]]
+    c.check(c.replay(reqs, sched), reqs)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

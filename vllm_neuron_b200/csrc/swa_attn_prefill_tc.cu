@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
                           const float* __restrict__ q, int ldq, const int32_t* __restrict__ block_table, int64_t bt_stride,
                           const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                           const int32_t* __restrict__ seq_pos0, void* __restrict__ out, int H, int G, int chunk, float scale,
-                          float softcap, const float* __restrict__ sig_bias, int out_f32, int split_p) {
+                          float softcap, const float* __restrict__ sig_bias, int out_f32, int split_p, int ny_tiles) {
   constexpr int NHK = DK / 64, NHV = DV / 64;
   constexpr int TQ = NHK * TP_HALF;                    // one query tile
   constexpr int TK = (MAPS ? 2 : 1) * NHK * TP_HALF;   // one key step (both maps' key heads with MAPS)
@@ -85,8 +85,17 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
   // ---- which rows, heads and keys this CTA owns (uniform over the CTA; a tile past its sequence's portion leaves at once)
   const int sq = blockIdx.z;
   const int t0 = seq_start[sq], n_new = seq_start[sq + 1] - t0;
-  const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * TP_BM;  // heaviest tiles of a causal launch first
-  if (q0 >= n_new) return;
+  // heaviest tiles first: a causal tile's cost grows with its index; with chunks of several tiles it grows with the tile's
+  // place INSIDE its chunk, so all chunks' last tiles go first, then their last but one, ... (grid y covers tiles_per_chunk x
+  // chunks >= ny_tiles places; the ones past the end leave)
+  const int tpc = chunk / TP_BM;
+  int tile = ny_tiles - 1 - (int)blockIdx.y;
+  if (tpc >= 2) {
+    const int nch = (ny_tiles + tpc - 1) / tpc;
+    tile = ((int)blockIdx.y % nch) * tpc + (tpc - 1 - (int)blockIdx.y / nch);
+  }
+  const int q0 = tile * TP_BM;
+  if (tile < 0 || tile >= ny_tiles || q0 >= n_new) return;
   const int pos0 = seq_pos0[sq];
   const int32_t* bt_row = block_table + (int64_t)seq_slot[sq] * bt_stride;
   int qhead[2], khead[2], vhead, ntile, Hv;
@@ -414,9 +423,11 @@ static int tp_launch(const CUtensorMap& km, const CUtensorMap& vm, const float* 
     attr_done = true;
   }
   const int rep = H / G;
-  dim3 grid(MAPS ? (G / 2) * rep : G * ((rep + 1) / 2), (max_new + TP_BM - 1) / TP_BM, B);
+  const int ny = (max_new + TP_BM - 1) / TP_BM, tpc = chunk / TP_BM;
+  const int gy = tpc >= 2 ? ((ny + tpc - 1) / tpc) * tpc : ny;  // the launch order of the kernel's tile map
+  dim3 grid(MAPS ? (G / 2) * rep : G * ((rep + 1) / 2), gy, B);
   B200_CUDA_OK(launch_kernel(kern, grid, dim3(TP_THREADS), smem, stream, km, vm, q, ldq, block_table, bt_stride, seq_start,
-                             seq_slot, seq_pos0, out, H, G, chunk, scale, softcap, sig_bias, out_f32, split_p));
+                             seq_slot, seq_pos0, out, H, G, chunk, scale, softcap, sig_bias, out_f32, split_p, ny));
   return B200_OK;
 }
 
