@@ -76,13 +76,15 @@ def test_grouped_norm_is_not_the_whole_row_norm():
     assert abs(h[0, 20].item() - 1.0) < 1e-4
 
 
-@pytest.mark.parametrize("ff,col0", [(24, 0), (100, 7), (1536, 64)])
-def test_polynomial_unit_rms_activation(ff, col0):
+@pytest.mark.parametrize("ff,col0,pad", [(24, 0, 3), (100, 7, 3), (1536, 64, 3),            # rows off the 16-byte grid: scalar kernel
+                                         (24, 0, 4), (36, 120, 0), (1536, 64, 0), (4100, 4, 0),   # the row-in-registers kernel
+                                         (20000, 0, 0)])                                          # too long for registers
+def test_polynomial_unit_rms_activation(ff, col0, pad):
     from oracle.zudarax_ref import poly_norm
 
     ops = _ops()
     g = torch.Generator().manual_seed(ff)
-    rows = torch.randn(6, col0 + ff + 3, generator=g) * 1.7
+    rows = torch.randn(6, col0 + ff + pad, generator=g) * 1.7
     coef = torch.tensor([0.7, -0.4, 0.25, 0.1])
     want = poly_norm(rows[:, col0:col0 + ff].double(), coef.double(), 1e-6)
     _close(ops.poly_norm(rows.to(DEV), col0, ff, coef.to(DEV), 1e-6, torch.float32), want, 3e-6)
@@ -135,6 +137,36 @@ def test_short_convolution_with_projection_bias_state_and_slot_reuse(taps):
         out = ops.causal_conv_silu(rows.to(DEV), col0, C, w.to(DEV), None, state, meta, torch.float32, in_bias=bias.to(DEV),
                                    silu=False)
         _close(out, torch.cat([want[k][at[k]:at[k] + n] for k, n in step]), 3e-6)
+        for k, n in step:
+            at[k] += n
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("taps", [2, 3, 4])
+def test_short_convolution_over_long_ragged_steps(taps, out_dtype):
+    """Channel counts and offsets in multiples of four take the kernel that carries the window in registers along a run of
+    tokens: sequences that start in the middle of a run, a one-token sequence between two long ones, and a second step that
+    continues all of them from the state."""
+    from oracle.zudarax_ref import short_conv
+
+    ops = _ops()
+    g = torch.Generator().manual_seed(10 + taps)
+    C, col0 = 72, 8
+    w = torch.randn(C, taps, generator=g)
+    bias = torch.randn(C, generator=g)
+    state = torch.full((3, taps - 1, C), -5.0, device=DEV)
+    lens = {"a": 700, "b": 2, "c": 900}
+    seqs = {k: torch.randn(n, col0 + C + 4, generator=g) for k, n in lens.items()}
+    want = {k: short_conv(u[:, col0:col0 + C].double() + bias.double(), w.double()) for k, u in seqs.items()}
+    slot = {"a": 1, "b": 0, "c": 2}
+    at = {k: 0 for k in seqs}
+    for step in ([("a", 301), ("b", 1), ("c", 498)], [("c", 402), ("b", 1), ("a", 399)]):
+        entries = [(slot[k], at[k], n) for k, n in step]
+        rows = torch.cat([seqs[k][at[k]:at[k] + n] for k, n in step])
+        meta = _meta(entries, {0: list(range(1, 40)), 1: list(range(40, 140)), 2: list(range(140, 260))})
+        out = ops.causal_conv_silu(rows.to(DEV), col0, C, w.to(DEV), None, state, meta, out_dtype, in_bias=bias.to(DEV), silu=False)
+        assert out.dtype == out_dtype
+        _close(out, torch.cat([want[k][at[k]:at[k] + n] for k, n in step]), 3e-6 if out_dtype == torch.float32 else 5e-3)
         for k, n in step:
             at[k] += n
 

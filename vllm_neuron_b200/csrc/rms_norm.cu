@@ -186,6 +186,60 @@ __global__ void poly_norm_kernel(const float* __restrict__ in, int ld, int col0,
   }
 }
 
+// The same with the row in registers: 16-byte loads, one pass over memory, the three sums reduced in one round, 8- or 16-byte
+// stores.  Needs n % 4 == 0, 16-byte aligned rows on both sides and n <= 4 * PN_VEC * blockDim.x.  The sums of a row do not
+// depend on what else is in the batch (one CTA per token, fixed order).
+constexpr int PN_VEC = 4;
+template <typename OT>
+__global__ void poly_norm_vec_kernel(const float* __restrict__ in, int ld, int col0, int n, const float* __restrict__ coef,
+                                     float eps, OT* __restrict__ out, int ldo) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ float red[3 * 32 + 3];
+  const int t = blockIdx.x, nv = n >> 2;
+  const float4* r = reinterpret_cast<const float4*>(in + (int64_t)t * ld + col0);
+  float4 z[PN_VEC];
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+#pragma unroll
+  for (int k = 0; k < PN_VEC; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    z[k] = i < nv ? r[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float q[4] = {z[k].x * z[k].x, z[k].y * z[k].y, z[k].z * z[k].z, z[k].w * z[k].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      s2 += q[j];
+      s4 += q[j] * q[j];
+      s6 += q[j] * q[j] * q[j];
+    }
+  }
+  s2 = warp_sum(s2), s4 = warp_sum(s4), s6 = warp_sum(s6);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = s2, red[32 + warp] = s4, red[64 + warp] = s6;
+  __syncthreads();
+  if (warp < 3) {
+    const float v = warp_sum(lane < nw ? red[warp * 32 + lane] : 0.f);
+    if (lane == 0) red[96 + warp] = v;
+  }
+  __syncthreads();
+  const float a = coef[0] / sqrtf(red[96] / (float)n + eps), b = coef[1] / sqrtf(red[97] / (float)n + eps),
+              c = coef[2] / sqrtf(red[98] / (float)n + eps), e = coef[3];
+  OT* o = out + (int64_t)t * ldo;
+#pragma unroll
+  for (int k = 0; k < PN_VEC; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i >= nv) continue;
+    const float v[4] = {z[k].x, z[k].y, z[k].z, z[k].w};
+    float y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) y[j] = a * v[j] + b * (v[j] * v[j]) + c * (v[j] * v[j] * v[j]) + e;
+    if constexpr (sizeof(OT) == 2) {
+      *reinterpret_cast<uint2*>(o + 4 * i) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+    } else {
+      *reinterpret_cast<float4*>(o + 4 * i) = make_float4(y[0], y[1], y[2], y[3]);
+    }
+  }
+}
+
 // Differential attention, closing step.  a fp32 [T][2 H][P] holds both maps' outputs: the kv group of `rep` output heads
 // stores its first maps in rows [2 rep g, 2 rep g + rep) and its second maps in the next rep rows.  One warp per (token,
 // output head): o = a1 - lambda a2;  out = o / sqrt(mean_P(o^2) + eps) * post * sigmoid(gate[h]).
@@ -319,6 +373,17 @@ int b200_poly_norm(const float* in, int ld, int col0, int n, const float* coef, 
                    void* stream) {
   B200_REQUIRE(in && coef && out && n >= 1 && ldo >= n, "poly_norm: null pointer or bad shape");
   if (T <= 0) return B200_OK;
+  const int es = out_dtype == B200_BF16 ? 2 : 4;
+  const bool vec = n % 4 == 0 && ld % 4 == 0 && col0 % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)in & 15) == 0 &&
+                   ((uintptr_t)out & (4 * es - 1)) == 0 && n <= 4 * PN_VEC * 1024;
+  if (vec) {  // the row in registers: a CTA of 128 .. 1024 threads (three warps reduce the three sums), four 16-byte loads each at most
+    int threads = 128;
+    while (threads * 4 * PN_VEC < n) threads *= 2;
+    B200_DISPATCH_ELEM(out_dtype, OT,
+                       B200_CUDA_OK(launch_kernel(poly_norm_vec_kernel<OT>, dim3(T), dim3(threads), 0, (cudaStream_t)stream, in, ld,
+                                                  col0, n, coef, eps, (OT*)out, ldo)));
+    return B200_OK;
+  }
   B200_DISPATCH_ELEM(out_dtype, OT,
                      B200_CUDA_OK(launch_kernel(poly_norm_kernel<OT>, dim3(T), dim3(n >= 1024 ? 256 : 128), 0, (cudaStream_t)stream,
                                                 in, ld, col0, n, coef, eps, (OT*)out, ldo)));

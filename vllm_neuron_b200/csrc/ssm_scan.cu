@@ -51,6 +51,73 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld, in
   }
 }
 
+// The same with four channels per thread (16-byte loads and stores) and the window of the last TAPS - 1 inputs carried in
+// registers along the run: one load per output instead of TAPS.  The window is filled from the rows before the run (or the
+// state, or zeros) at the run's first token and wherever a new sequence starts inside the run.  Sums in the order of the
+// kernel above.  Needs C, col0 and ld multiples of 4 and 16-byte aligned bases.
+template <typename OT, int TAPS>
+__global__ void causal_conv_vec_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ cw,
+                                       const float* __restrict__ cb, const float* __restrict__ in_bias, int silu,
+                                       const float* __restrict__ state, const int32_t* __restrict__ tok_seq,
+                                       const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
+                                       const int32_t* __restrict__ seq_pos0, OT* __restrict__ out, int T, int C, int run) {
+  griddep_launch();
+  griddep_wait();
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= C) return;
+  float w[4][TAPS], bias[4], ib[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    bias[k] = cb ? cb[c + k] : 0.f;
+    ib[k] = in_bias ? in_bias[c + k] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) w[k][j] = cw[(int64_t)(c + k) * TAPS + j];
+  }
+  float win[TAPS > 1 ? TAPS - 1 : 1][4];
+  const int t_begin = blockIdx.y * run, t_end = min(T, t_begin + run);
+  int prev_s = -1;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int s = tok_seq[t];
+    if (s != prev_s) {
+      prev_s = s;
+      const int i = t - seq_start[s];
+      const bool has_state = seq_pos0[s] > 0;
+      const float* st = state + (int64_t)seq_slot[s] * (TAPS - 1) * C;
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) {
+        const int src = i - (TAPS - 1 - j);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src >= 0) {
+          v = *reinterpret_cast<const float4*>(in + (int64_t)(t - (TAPS - 1 - j)) * ld + col0 + c);
+          v.x += ib[0], v.y += ib[1], v.z += ib[2], v.w += ib[3];
+        } else if (has_state) {
+          v = *reinterpret_cast<const float4*>(st + (int64_t)(src + TAPS - 1) * C + c);
+        }
+        win[j][0] = v.x, win[j][1] = v.y, win[j][2] = v.z, win[j][3] = v.w;
+      }
+    }
+    const float4 u = *reinterpret_cast<const float4*>(in + (int64_t)t * ld + col0 + c);
+    const float cur[4] = {u.x + ib[0], u.y + ib[1], u.z + ib[2], u.w + ib[3]};
+    float y[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float acc = bias[k];
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) acc += win[j][k] * w[k][j];
+      acc += cur[k] * w[k][TAPS - 1];
+      y[k] = silu ? silu_f(acc) : acc;
+#pragma unroll
+      for (int j = 0; j + 1 < TAPS - 1; ++j) win[j][k] = win[j + 1][k];
+      if (TAPS > 1) win[TAPS - 2][k] = cur[k];
+    }
+    if constexpr (sizeof(OT) == 2) {
+      *reinterpret_cast<uint2*>(out + (int64_t)t * C + c) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+    } else {
+      *reinterpret_cast<float4*>(out + (int64_t)t * C + c) = make_float4(y[0], y[1], y[2], y[3]);
+    }
+  }
+}
+
 // new state = the last (taps - 1) inputs of [old state | this step's inputs]; one thread per (sequence, channel) reads
 // everything it needs before it writes, so the update is in place.  Runs after causal_conv_silu_kernel on the stream.
 __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ in_bias,
@@ -342,6 +409,21 @@ int b200_causal_conv(const float* in, int ld, int col0, const float* conv_w, con
   if (T <= 0 || B <= 0) return B200_OK;
   const int th = 128;
   const int run = T / 256 < 1 ? 1 : T / 256 > CONV_RUN ? CONV_RUN : T / 256;
+  const int oes = out_dtype == B200_BF16 ? 2 : 4;
+  const bool vec = taps >= 2 && taps <= 4 && C % 4 == 0 && col0 % 4 == 0 && ld % 4 == 0 && ((uintptr_t)in & 15) == 0 &&
+                   ((uintptr_t)state & 15) == 0 && ((uintptr_t)out & (4 * oes - 1)) == 0;
+  if (vec) {
+    const dim3 grid((C / 4 + th - 1) / th, (T + run - 1) / run);
+#define CONV_VEC(TAPS_)                                                                                                          \
+  B200_DISPATCH_ELEM(out_dtype, OT,                                                                                              \
+                     B200_CUDA_OK(launch_kernel(causal_conv_vec_kernel<OT, TAPS_>, grid, dim3(th), 0, (cudaStream_t)stream, in, ld, \
+                                                col0, conv_w, conv_b, in_bias, silu, (const float*)state, tok_seq, seq_start,    \
+                                                seq_slot, seq_pos0, (OT*)out, T, C, run)))
+    if (taps == 2) CONV_VEC(2);
+    else if (taps == 3) CONV_VEC(3);
+    else CONV_VEC(4);
+#undef CONV_VEC
+  } else
   B200_DISPATCH_ELEM(out_dtype, OT,
                      B200_CUDA_OK(launch_kernel(causal_conv_silu_kernel<OT>, dim3((C + th - 1) / th, (T + run - 1) / run), dim3(th), 0,
                                                 (cudaStream_t)stream, in, ld, col0, conv_w, conv_b, in_bias, silu, (const float*)state,
