@@ -365,7 +365,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
                                int out_f32, int split_p, void* stream);
 /* Prompt portions on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory): same ragged step arguments as
  * b200_swa_sink_attn_prefill, no sink and no window.  Kernels exist for pages of 32 tokens and D = Dv = 64 or 128 (softmax,
- * capped softmax, sigmoid weights) and, with v_div = 2, D = 64 with Dv = 64 or 128 (softmax); q rows must be 16-byte aligned.
+ * capped softmax, sigmoid weights) and, with v_div = 2, D = 32 or 64 with Dv = 64 or 128 (softmax); q rows must be 16-byte aligned.
  * b200_swa_sink_attn_prefill_tc_supported says whether a combination has one; the launch returns B200_ERR_UNSUPPORTED
  * otherwise.  num_blocks = pages of the pools. */
 int b200_swa_sink_attn_prefill_tc_supported(int D, int Dv, int block_size, int v_div, int capped, int sigmoid);

@@ -382,6 +382,8 @@ TC_CASES = {
     "sigmoid 64": (2, 1, 1, 64, 64, {"sigmoid": True}),
     "two maps, values of 128": (8, 4, 2, 64, 128, {"out_f32": True}),
     "two maps, values of 64": (12, 4, 2, 64, 64, {"out_f32": True}),
+    "two maps of 32, values of 64": (8, 4, 2, 32, 64, {"out_f32": True}),
+    "two maps of 32, values of 128, one kv group": (6, 2, 1, 32, 128, {"out_f32": True}),
 }
 
 

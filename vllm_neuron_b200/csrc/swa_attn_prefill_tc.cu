@@ -11,7 +11,8 @@
 //     device arrays), and a tile starts at the key step that holds the first key of its first row's chunk;
 //   * q arrives as fp32 rows: the softmax warpgroups round it to bf16 and lay it into the 128-byte-swizzled operand
 //     layout themselves;
-//   * key size and value size are separate template parameters, and with MAPS the two tiles of a CTA are the two score
+//   * key size and value size are separate template parameters (keys of 32 columns are 64-byte rows under the 64B swizzle),
+//     and with MAPS the two tiles of a CTA are the two score
 //     maps of ONE query head: each has its own key head (2g, 2g + 1), both multiply the same value step;
 //   * the weights enter the second product as TWO bf16 terms, hi = bf16(p) in the first 64 columns the scores occupied and
 //     lo = bf16(p - hi) in the other 64 (16 mantissa bits; the scores sit in registers by then), two MMAs per 16 keys;
@@ -40,6 +41,16 @@ __device__ __forceinline__ uint64_t tp_desc_mn_sw128(uint32_t smem_addr, uint32_
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
+  return d;
+}
+// K-major, 64B-swizzled operand tile: rows of 64 B, 8-row groups 512 B apart
+__device__ __forceinline__ uint64_t tp_desc_sw64(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;  // SWIZZLE_64B
   return d;
 }
 __device__ __forceinline__ void tp_ld_x32(uint32_t taddr, uint32_t* v) {
@@ -74,9 +85,12 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
                           const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                           const int32_t* __restrict__ seq_pos0, void* __restrict__ out, int H, int G, int chunk, float scale,
                           float softcap, const float* __restrict__ sig_bias, int out_f32, int split_p, int ny_tiles) {
-  constexpr int NHK = DK / 64, NHV = DV / 64;
-  constexpr int TQ = NHK * TP_HALF;                    // one query tile
-  constexpr int TK = (MAPS ? 2 : 1) * NHK * TP_HALF;   // one key step (both maps' key heads with MAPS)
+  // q / k operand rows: pieces of 64 columns (128 bytes, 128B swizzle), or one piece of 32 columns (64 bytes, 64B swizzle)
+  constexpr int KROW = DK >= 64 ? 128 : DK * 2;
+  constexpr int NHK = DK >= 64 ? DK / 64 : 1, NHV = DV / 64;
+  constexpr int HALFK = TP_BN * KROW;                  // one [128 rows x KROW bytes] piece
+  constexpr int TQ = NHK * HALFK;                      // one query tile
+  constexpr int TK = (MAPS ? 2 : 1) * NHK * HALFK;     // one key step (both maps' key heads with MAPS)
   constexpr int TV = NHV * TP_HALF;                    // one value step
   constexpr uint32_t IDESC_S = umma_idesc(1, 1, TP_BM, TP_BN);
   constexpr uint32_t IDESC_PV = umma_idesc(1, 1, TP_BM, DV) | (1u << 16);  // B (= V) is MN-major
@@ -174,6 +188,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
         uint64_t* full = is_k ? k_full : v_full;
         uint64_t* empty = is_k ? k_empty : v_empty;
         const int tile = is_k ? TK : TV, nh = is_k ? NHK : NHV, heads = is_k ? G : Hv;
+        const int piece = is_k ? HALFK : TP_HALF, rowb = is_k ? KROW : 128;
         const int nm = (is_k && MAPS) ? 2 : 1;
         for (int it = 0; it < niter; ++it) {
           const int s = it % TP_ST, j = j_lo + it;
@@ -187,7 +202,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
             for (int m = 0; m < nm; ++m) {
               const int row = (blk * heads + (is_k ? khead[m] : vhead)) * TP_BLK;
               for (int h = 0; h < nh; ++h)
-                tma_load_2d(dst + (m * nh + h) * TP_HALF + b * (TP_BLK * 128), map, &full[s], h * 64, row);
+                tma_load_2d(dst + (m * nh + h) * piece + b * (TP_BLK * rowb), map, &full[s], h * 64, row);
             }
           }
         }
@@ -197,12 +212,17 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
       // ---------------------------------------------------------------- MMA issuer
       if (lane == 0) {
         auto issue_s = [&](int t, int s) {
-          const uint32_t qa = smem_u32(q_s + t * TQ), ka = smem_u32(k_s + (size_t)s * TK + (MAPS ? t * NHK * TP_HALF : 0));
+          const uint32_t qa = smem_u32(q_s + t * TQ), ka = smem_u32(k_s + (size_t)s * TK + (MAPS ? t * NHK * HALFK : 0));
+          constexpr int PER = KROW / 32;  // 16-column MMA steps per row piece
 #pragma unroll
           for (int kk = 0; kk < DK / 16; ++kk) {
-            const uint32_t off = (uint32_t)(kk >> 2) * TP_HALF + (uint32_t)(kk & 3) * 32;
-            umma_ss<KIND_F16>(tmem_base + (uint32_t)t * 128u, umma_desc_sw128(qa + off), umma_desc_sw128(ka + off), IDESC_S,
-                              (uint32_t)(kk != 0));
+            const uint32_t off = (uint32_t)(kk / PER) * HALFK + (uint32_t)(kk % PER) * 32;
+            if (DK >= 64)
+              umma_ss<KIND_F16>(tmem_base + (uint32_t)t * 128u, umma_desc_sw128(qa + off), umma_desc_sw128(ka + off), IDESC_S,
+                                (uint32_t)(kk != 0));
+            else
+              umma_ss<KIND_F16>(tmem_base + (uint32_t)t * 128u, tp_desc_sw64(qa + off), tp_desc_sw64(ka + off), IDESC_S,
+                                (uint32_t)(kk != 0));
           }
           tc_commit(&s_full[t]);
         };
@@ -263,7 +283,10 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
             const float4 b = *reinterpret_cast<const float4*>(qsrc + (int64_t)row * ldq + c * 8 + 4);
             w.x = pack_bf16(a.x, a.y), w.y = pack_bf16(a.z, a.w), w.z = pack_bf16(b.x, b.y), w.w = pack_bf16(b.z, b.w);
           }
-          *reinterpret_cast<uint4*>(qd + (c >> 3) * TP_HALF + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = w;
+          if (DK >= 64)  // 128B swizzle: 16-byte piece c of row r sits at piece c ^ (r % 8)
+            *reinterpret_cast<uint4*>(qd + (c >> 3) * HALFK + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = w;
+          else           // 64B swizzle: at piece c ^ ((r / 2) % 4)
+            *reinterpret_cast<uint4*>(qd + row * KROW + ((c ^ ((row >> 1) & 3)) << 4)) = w;
         }
         fence_proxy_async();  // the tensor core reads these bytes through the async proxy
         mbar_arrive(q_full);
@@ -415,7 +438,7 @@ static int tp_launch(const CUtensorMap& km, const CUtensorMap& vm, const float* 
   auto kern = swa_prefill_tc_kernel<DK, DV, KIND, MAPS>;
   // operand tiles + barriers + alignment slack; never less than half an SM's shared memory, so that one CTA (which takes all
   // 512 columns of tensor memory) is resident per SM
-  size_t smem = (size_t)(2 + TP_ST * (MAPS ? 2 : 1)) * (DK / 64) * TP_HALF + (size_t)TP_ST * (DV / 64) * TP_HALF + 256 + 1024;
+  size_t smem = (size_t)(2 + TP_ST * (MAPS ? 2 : 1)) * TP_BN * DK * 2 + (size_t)TP_ST * (DV / 64) * TP_HALF + 256 + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
   static bool attr_done = false;
   if (!attr_done) {
@@ -441,7 +464,7 @@ extern "C" {
 int b200_swa_sink_attn_prefill_tc_supported(int D, int Dv, int block_size, int v_div, int capped, int sigmoid) {
   if (block_size != TP_BLK || (capped && sigmoid)) return 0;
   if (v_div == 1) return (D == 64 && Dv == 64) || (D == 128 && Dv == 128);
-  if (v_div == 2) return !capped && !sigmoid && D == 64 && (Dv == 64 || Dv == 128);
+  if (v_div == 2) return !capped && !sigmoid && (D == 32 || D == 64) && (Dv == 64 || Dv == 128);
   return 0;
 }
 
@@ -461,7 +484,10 @@ int b200_swa_sink_attn_prefill_tc(const float* q, int ldq, const void* k_pool, c
   }
   if (B <= 0 || max_new <= 0) return B200_OK;
   CUtensorMap km, vm;
-  int rc = kv_pool_tmap(k_pool, num_blocks, G, D, &km);
+  // key rows of 32 columns are 64 bytes: boxes of 32 columns x 32 rows under the 64B swizzle
+  int rc = D == 32 ? make_tmap_2d_sw64(&km, k_pool, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 32, (uint64_t)num_blocks * G * TP_BLK, 64, 32,
+                                       TP_BLK)
+                   : kv_pool_tmap(k_pool, num_blocks, G, D, &km);
   if (rc) return rc;
   rc = kv_pool_tmap(v_pool, num_blocks, G / v_div, Dv, &vm);
   if (rc) return rc;
@@ -469,6 +495,10 @@ int b200_swa_sink_attn_prefill_tc(const float* q, int ldq, const void* k_pool, c
 #define TP_GO(DK_, DV_, KIND_, MAPS_)                                                                                          \
   return tp_launch<DK_, DV_, KIND_, MAPS_>(km, vm, q, ldq, block_table, bt_stride, seq_start, seq_slot, seq_pos0, B, max_new, \
                                            out, H, G, chunk, scale, softcap, sigmoid_bias, out_f32, split_p, st)
+  if (v_div == 2 && D == 32) {
+    if (Dv == 64) TP_GO(32, 64, TP_SOFTMAX, true);
+    TP_GO(32, 128, TP_SOFTMAX, true);
+  }
   if (v_div == 2) {
     if (Dv == 64) TP_GO(64, 64, TP_SOFTMAX, true);
     TP_GO(64, 128, TP_SOFTMAX, true);
