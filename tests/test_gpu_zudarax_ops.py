@@ -175,7 +175,8 @@ def test_short_convolution_over_long_ragged_steps(taps, out_dtype):
 @pytest.mark.parametrize("kv_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("half,normed,scaling", [(True, True, None), (True, False, {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 1.0}),
                                                  (False, True, {"factor": 3.0, "original": 32, "fast": 8.0, "slow": 2.0})])
-def test_whole_projection_norm_rotation_and_cache_write(kv_dtype, half, normed, scaling):
+@pytest.mark.parametrize("lead", [3, 4])   # columns before q: 3 puts the rows off the 16-byte grid (scalar kernel), 4 on it
+def test_whole_projection_norm_rotation_and_cache_write(kv_dtype, half, normed, scaling, lead):
     from oracle.zudarax_ref import rms_unit, rotate_half
     from vllm_neuron_b200.hybrid import RotSpec
 
@@ -183,7 +184,7 @@ def test_whole_projection_norm_rotation_and_cache_write(kv_dtype, half, normed, 
     g = torch.Generator().manual_seed(11)
     H, G, Gv, D, Dv, rot_n, bs, eps = 5, 2, 1, 24, 20, 16, 8, 1e-5
     pos0, n = 37, 13                                                          # positions that cross page borders
-    rows = torch.randn(n, 3 + H * D + G * D + Gv * Dv, generator=g)
+    rows = torch.randn(n, lead + H * D + G * D + Gv * Dv, generator=g)
     qn, kn = 1 + 0.3 * torch.randn(H * D, generator=g), 1 + 0.3 * torch.randn(G * D, generator=g)
     rot = {"dims": rot_n, "base": 300.0, "scaling": scaling}
     cos, sin = (t.to(DEV) for t in RotSpec(rot_n, 300.0, scaling).tables(64))
@@ -191,11 +192,11 @@ def test_whole_projection_norm_rotation_and_cache_write(kv_dtype, half, normed, 
     meta = _meta([(0, pos0, n)], {0: pages}, bs)
     k_pool = torch.zeros(8, G, bs, D, dtype=kv_dtype, device=DEV)
     v_pool = torch.zeros(8, Gv, bs, Dv, dtype=kv_dtype, device=DEV)
-    q = ops.qk_norm_rope_kv_write(rows.to(DEV), 3, 3 + H * D, 3 + H * D + G * D, H, k_pool, v_pool, meta,
+    q = ops.qk_norm_rope_kv_write(rows.to(DEV), lead, lead + H * D, lead + H * D + G * D, H, k_pool, v_pool, meta,
                                   q_norm=qn.to(DEV) if normed else None, k_norm=kn.to(DEV) if normed else None, eps=eps, rot_n=rot_n,
                                   rot_half=half, cos=cos, sin=sin)
     r = rows.double()
-    rq, rk, rv = r[:, 3:3 + H * D], r[:, 3 + H * D:3 + H * D + G * D], r[:, 3 + H * D + G * D:]
+    rq, rk, rv = r[:, lead:lead + H * D], r[:, lead + H * D:lead + H * D + G * D], r[:, lead + H * D + G * D:]
     if normed:                                                                # over all heads' columns at once
         rq, rk = rms_unit(rq, eps) * qn.double(), rms_unit(rk, eps) * kn.double()
 

@@ -131,6 +131,108 @@ __global__ void qk_norm_rope_kv_write_kernel(const float* __restrict__ src, int 
   }
 }
 
+// The same with four columns per thread and step (16-byte loads; 8- or 16-byte stores): needs every column offset, head size
+// and the row pitch in multiples of four, a rotating part whose pairs fall into whole groups of four (rot_n % 8 == 0 for the
+// half layout, % 4 for neighbours) and 16-byte aligned bases.  One division per four columns.
+template <typename KT>
+__global__ void qk_norm_rope_kv_write_vec_kernel(const float* __restrict__ src, int ld, int q_col0, int k_col0, int v_col0,
+                                                 const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                                 int rot_n, int rot_half, const float* __restrict__ cos_t,
+                                                 const float* __restrict__ sin_t, const int32_t* __restrict__ tok_pos,
+                                                 const int64_t* __restrict__ slots, float* __restrict__ q_out,
+                                                 KT* __restrict__ k_pool, KT* __restrict__ v_pool, int H, int G, int Gv, int D, int Dv,
+                                                 int bs) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ float red[2][33];
+  const int t = blockIdx.x;
+  const float* row = src + (int64_t)t * ld;
+  const int nq = H * D, nk = G * D;
+  auto ld4 = [](const float* p) { return *reinterpret_cast<const float4*>(p); };
+  float inv_q = 1.0f, inv_k = 1.0f;
+  if (q_norm || k_norm) {
+    float sq = 0.f, sk = 0.f;
+    if (q_norm)
+      for (int i = threadIdx.x * 4; i < nq; i += blockDim.x * 4) {
+        const float4 a = ld4(row + q_col0 + i);
+        sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      }
+    if (k_norm)
+      for (int i = threadIdx.x * 4; i < nk; i += blockDim.x * 4) {
+        const float4 a = ld4(row + k_col0 + i);
+        sk += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if ((threadIdx.x & 31) == 0) {
+      red[0][threadIdx.x >> 5] = sq;
+      red[1][threadIdx.x >> 5] = sk;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int nw = (blockDim.x + 31) >> 5;
+      float a = threadIdx.x < nw ? red[0][threadIdx.x] : 0.f, b = threadIdx.x < nw ? red[1][threadIdx.x] : 0.f;
+      a = warp_sum(a);
+      b = warp_sum(b);
+      if (threadIdx.x == 0) {
+        red[0][32] = a;
+        red[1][32] = b;
+      }
+    }
+    __syncthreads();
+    if (q_norm) inv_q = 1.0f / sqrtf(red[0][32] / (float)nq + eps);
+    if (k_norm) inv_k = 1.0f / sqrtf(red[1][32] / (float)nk + eps);
+  }
+  const int pos = tok_pos[t];
+  const int half = rot_n >> 1;
+  const float* cs = cos_t + (int64_t)pos * half;
+  const float* sn = sin_t + (int64_t)pos * half;
+  const int64_t slot = slots[t];
+  const int64_t blk = slot / bs, off = slot % bs;
+  // columns i .. i + 3 of a projection after norm and rotation; d = i % D
+  auto normed = [&](int col0, const float* nw, float inv, int i) -> float4 {
+    float4 u = ld4(row + col0 + i);
+    if (nw) {
+      const float4 w = ld4(nw + i);
+      u.x *= inv * w.x, u.y *= inv * w.y, u.z *= inv * w.z, u.w *= inv * w.w;
+    }
+    return u;
+  };
+  auto turned = [&](int col0, const float* nw, float inv, int i, int d) -> float4 {
+    const float4 u = normed(col0, nw, inv, i);
+    if (d >= rot_n) return u;
+    if (rot_half) {
+      const bool first = d < half;
+      const int idx = first ? d : d - half;
+      const float4 o = normed(col0, nw, inv, first ? i + half : i - half);
+      const float4 c = ld4(cs + idx), s = ld4(sn + idx);
+      if (first) return make_float4(u.x * c.x - o.x * s.x, u.y * c.y - o.y * s.y, u.z * c.z - o.z * s.z, u.w * c.w - o.w * s.w);
+      return make_float4(u.x * c.x + o.x * s.x, u.y * c.y + o.y * s.y, u.z * c.z + o.z * s.z, u.w * c.w + o.w * s.w);
+    }
+    const int idx = d >> 1;
+    const float c0 = cs[idx], s0 = sn[idx], c1 = cs[idx + 1], s1 = sn[idx + 1];
+    return make_float4(u.x * c0 - u.y * s0, u.y * c0 + u.x * s0, u.z * c1 - u.w * s1, u.w * c1 + u.z * s1);
+  };
+  auto put = [](KT* p, float4 v) {
+    if constexpr (sizeof(KT) == 2) {
+      *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+    } else {
+      *reinterpret_cast<float4*>(p) = v;
+    }
+  };
+  for (int i = threadIdx.x * 4; i < nq; i += blockDim.x * 4)
+    *reinterpret_cast<float4*>(q_out + (int64_t)t * nq + i) = turned(q_col0, q_norm, inv_q, i, i % D);
+  if (slot < 0) return;
+  for (int i = threadIdx.x * 4; i < nk; i += blockDim.x * 4) {
+    const int g = i / D, d = i - g * D;
+    put(k_pool + ((blk * G + g) * bs + off) * D + d, turned(k_col0, k_norm, inv_k, i, d));
+  }
+  for (int i = threadIdx.x * 4; i < Gv * Dv; i += blockDim.x * 4) {
+    const int g = i / Dv, d = i - g * Dv;
+    put(v_pool + ((blk * Gv + g) * bs + off) * Dv + d, ld4(row + v_col0 + i));
+  }
+}
+
 constexpr int ATT_WARPS = 16;  // the launch is bound by load latency: every warp walks few key tiles, many are in flight
 
 // QH query rows (fp32, shared memory, pitch D) . one k row, with 16-byte loads when the row allows it: the key row is
@@ -409,6 +511,20 @@ int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0,
                "qk_norm_rope_kv_write: %d rotating columns in heads of %d", rot_n, D);
   B200_REQUIRE(H >= 1 && G >= 1 && Gv >= 1 && D >= 1 && Dv >= 1, "qk_norm_rope_kv_write: bad shape");
   if (T <= 0) return B200_OK;
+  auto a16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = D % 4 == 0 && Dv % 4 == 0 && ld % 4 == 0 && q_col0 % 4 == 0 && k_col0 % 4 == 0 && v_col0 % 4 == 0 &&
+                   rot_n % (rot_half ? 8 : 4) == 0 && a16(src) && a16(q_out) && a16(k_pool) && a16(v_pool) && a16(q_norm) &&
+                   a16(k_norm) && a16(cos_table) && a16(sin_table);
+  if (vec) {
+    const int cols = H * D > G * D ? H * D : G * D;
+    const int threads = cols >= 1024 ? 256 : cols >= 512 ? 128 : 64;
+    B200_DISPATCH_ELEM(kv_dtype, KT,
+                       B200_CUDA_OK(launch_kernel(qk_norm_rope_kv_write_vec_kernel<KT>, dim3(T), dim3(threads), 0, (cudaStream_t)stream,
+                                                  src, ld, q_col0, k_col0, v_col0, q_norm, k_norm, eps, rot_n, rot_half, cos_table,
+                                                  sin_table, tok_pos, slot_mapping, q_out, (KT*)k_pool, (KT*)v_pool, H, G, Gv, D, Dv,
+                                                  block_size)));
+    return B200_OK;
+  }
   B200_DISPATCH_ELEM(kv_dtype, KT,
                      B200_CUDA_OK(launch_kernel(qk_norm_rope_kv_write_kernel<KT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, src, ld,
                                                 q_col0, k_col0, v_col0, q_norm, k_norm, eps, rot_n, rot_half, cos_table, sin_table,
