@@ -68,12 +68,12 @@ def cfg_d():
     yarn = {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0}
     return {"architecture": "Zudarax", "vocab": 160, "width": 128, "norm": {"eps": 1e-6, "groups": 2}, "layers": [
         _layer("attention_2", 96, heads=2, kv_heads=1, dim=64, vdim=128, diff=0.4, scale=0.125, rot=_rot(16, 10000.0)),
-        _layer("attention", 64, heads=3, kv_heads=1, dim=128, vdim=128, conv=3, scale=0.09, softcap=8.0, mask={"size": 72},
-               rot=_rot(64, 20000.0)),
+        _layer("attention", 64, heads=3, kv_heads=1, dim=128, vdim=128, conv=5, scale=0.09, softcap=8.0, mask={"size": 72},
+               rot=_rot(64, 30000.0)),
         _layer("attention_3", 64, heads=4, kv_heads=2, dim=64, vdim=64, conv=2, scale=0.125, rot=_rot(64, 1000.0, yarn)),
         _layer("attention_2", None, heads=4, kv_heads=2, dim=64, vdim=64, diff=0.7, scale=0.125, rot=_rot(32, 500.0)),
         _layer("attention", 64, heads=2, kv_heads=2, dim=64, vdim=64, scale=0.125, rot=_rot(8, 100.0)),
-        _layer("attention_3", None, heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, rot=_rot(32, 250000.0)),
+        _layer("attention_3", None, heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, rot=_rot(32, 120000.0)),
     ]}
 
 
