@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 11
+#define B200_ABI_VERSION 12
 
 enum {
   B200_OK = 0,
@@ -48,7 +48,7 @@ enum {
 enum { B200_BF16 = 0, B200_FP8_E4M3 = 1, B200_INT8 = 2, B200_F32 = 3, B200_INT8_WO = 4 };
 /* gate activations of a gated-linear unit, and how a router turns its chosen logits into weights */
 enum { B200_ACT_SWISH_CLAMPED = 0, B200_ACT_SILU = 1, B200_ACT_GELU_TANH = 2 };
-enum { B200_ROUTE_SIGMOID = 0, B200_ROUTE_SOFTMAX_TOP = 1 };
+enum { B200_ROUTE_SIGMOID = 0, B200_ROUTE_SOFTMAX_TOP = 1, B200_ROUTE_SOFTMAX_RENORM = 2 };
 
 int b200_abi_version(void);
 const char* b200_last_error(void);
@@ -347,12 +347,23 @@ int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* 
  * sigmoid(s + sigmoid_bias[h]) with no normalisation over keys (no sink then); v_div >= 1: key head g reads value head
  * g / v_div of a value pool with G / v_div heads; out_f32: fp32 output rows whatever kv_dtype.
  * splits > 1: that many CTAs share a (token, head block)'s keys and a second launch merges their partial results from
- * split_workspace fp32 [T * H * splits * (Dv + 2)] (long contexts at small batch: more CTAs than one per token and head block). */
+ * split_workspace fp32 [T * H * splits * (Dv + 2)] (long contexts at small batch: more CTAs than one per token and head block).
+ * pool > 0 (with a window): beside the window's keys a query at position i sees ONE key / value for every block b of `pool`
+ * positions that lies wholly before its window, b pool + pool - 1 <= i - window -- the block's rows of pooled_k / pooled_v
+ * (b200_kv_pool_mean); blocks and keys share the softmax. */
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
                        int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
                        float softcap, const float* sigmoid_bias, int v_div, int out_f32, int splits, float* split_workspace,
-                       void* stream);
+                       const void* pooled_k, const void* pooled_v, int pool, void* stream);
+/* Means of the key / value blocks that the step completes: for every token t of the step whose position closes a block of `pool`
+ * positions (tok_pos[t] % pool == pool - 1; slot_mapping[t] >= 0) the block's `pool` key and value rows are read back from the
+ * pools through block-table row tok_row[t], summed in fp32, divided by `pool` and written to
+ * pooled_k [num_blocks][G][ppb][D] / pooled_v [num_blocks][Gv][ppb][Dv], ppb = ceil(block_size / pool): the entry of a block lives
+ * in the page of the block's last position e, at index (e % block_size) / pool.  Run it after the step's keys are written. */
+int b200_kv_pool_mean(const void* k_pool, const void* v_pool, void* pooled_k, void* pooled_v, int kv_dtype,
+                      const int32_t* block_table, int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos,
+                      const int64_t* slot_mapping, int T, int G, int Gv, int D, int Dv, int block_size, int pool, void* stream);
 /* The same attention for prompt portions on the tensor cores (bf16 pools; D and Dv multiples of 16, Dv <= 256, else
  * B200_ERR_UNSUPPORTED): sequence s brings tokens [seq_start[s], seq_start[s+1]) at positions seq_pos0[s].., block-table row
  * seq_slot[s]; max_new = the longest portion of the step.  q is rounded to bf16; softmax and accumulation are fp32.
@@ -362,7 +373,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
                                int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
                                int Dv, int v_pitch, int block_size, int chunk, float softcap, const float* sigmoid_bias, int v_div,
-                               int out_f32, int split_p, void* stream);
+                               int out_f32, int split_p, const void* pooled_k, const void* pooled_v, int pool, void* stream);
 /* Prompt portions on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory): same ragged step arguments as
  * b200_swa_sink_attn_prefill, no sink and no window.  Kernels exist for pages of 32 tokens and D = Dv = 64 or 128 (softmax,
  * capped softmax, sigmoid weights) and, with v_div = 2, D = 32 or 64 with Dv = 64 or 128 (softmax); q rows must be 16-byte aligned.
@@ -381,7 +392,7 @@ int b200_swa_sink_attn_decode_tc(const float* q, int ldq, const void* k_pool, co
                                  int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
                                  int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
                                  float softcap, const float* sigmoid_bias, int v_div, int out_f32, int split_p, int splits,
-                                 float* split_workspace, void* stream);
+                                 float* split_workspace, const void* pooled_k, const void* pooled_v, int pool, void* stream);
 /* Merge of key splits: part fp32 [rows][splits][2 + Dv] = {maximum, denominator, unnormalised accumulator} per split ->
  * out [rows][Dv] (fp32 when out_f32, else out_dtype); sigmoid: plain sums, no denominator. */
 int b200_attn_split_merge(const float* part, int splits, int Dv, int sigmoid, int out_f32, int out_dtype, void* out, int64_t rows,
@@ -390,15 +401,17 @@ int b200_attn_split_merge(const float* part, int splits, int Dv, int sigmoid, in
  * q_col0, k [G][D] at k_col0, v [Gv][Dv] at v_col0.  q_norm / k_norm fp32 [H * D] / [G * D] (or NULL): RMS norm over the WHOLE
  * projection, times the weight.  The first rot_n columns of every q and k head turn by tok_pos[t]: pairs (i, i + rot_n / 2) when
  * rot_half, else (2i, 2i + 1); (u, v) -> (u cos - v sin, v cos + u sin), cos / sin fp32 tables [positions][rot_n / 2].
- * q -> q_out fp32 [T][H * D]; k, v -> pools K [num_blocks][G][block_size][D], V [num_blocks][Gv][block_size][Dv] by slot. */
+ * q -> q_out fp32 [T][H * D], head h times q_head_scale[h] when given (a per-head temperature of the scores);
+ * k, v -> pools K [num_blocks][G][block_size][D], V [num_blocks][Gv][block_size][Dv] by slot. */
 int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0, int v_col0, const float* q_norm,
                                const float* k_norm, float eps, int rot_n, int rot_half, const float* cos_table,
                                const float* sin_table, const int32_t* tok_pos, const int64_t* slot_mapping, float* q_out,
                                void* k_pool, void* v_pool, int kv_dtype, int T, int H, int G, int Gv, int D, int Dv, int block_size,
-                               void* stream);
+                               const float* q_head_scale, void* stream);
 /* Router decision over fp32 logits [T] rows of pitch ld (+ bias fp32 [E] when given): the `top` largest (ties to the lower
  * index); weights = sigmoid of each chosen logit, no renormalisation (B200_ROUTE_SIGMOID), or the softmax over the chosen
- * logits only (B200_ROUTE_SOFTMAX_TOP). */
+ * logits only (B200_ROUTE_SOFTMAX_TOP), or the softmax over ALL experts with the chosen scores divided by their sum + 1e-20
+ * (B200_ROUTE_SOFTMAX_RENORM). */
 int b200_moe_topk(const float* logits, int ld, const float* bias, int mode, int32_t* topk_idx, float* topk_weight, int T, int E,
                   int top, void* stream);
 /* rows per expert tile of b200_moe_align / b200_grouped_linear; four times as many (tile_rows = 4 x this) are taken for
@@ -444,7 +457,8 @@ int b200_rms_residual(float* x, const float* y, int nsum, const float* y_weight,
 /* out[t][0..n) = v / sqrt(mean(v^2) + eps) * (offset + w), v = columns [col0, col0 + n) of the fp32 rows `in` (pitch ld) */
 int b200_rmsnorm_cols(const float* in, int ld, int col0, int n, const float* w, float offset, float eps, void* out, int out_dtype,
                       int ldo, int T, void* stream);
-/* o fp32 [T][H][P]: out = o / sqrt(mean_P(o^2) + eps) * w[0..P) * silu(gate), gate = columns gate_col0.. of fp32 rows (pitch ldg) */
+/* o fp32 [T][H][P]: out = o / sqrt(mean_P(o^2) + eps) * w[0..P) * silu(gate), gate = columns gate_col0.. of fp32 rows (pitch ldg);
+ * gate NULL: the norm alone */
 int b200_head_rmsnorm_gate(const float* o, const float* gate, int ldg, int gate_col0, const float* w, float eps, void* out,
                            int out_dtype, int T, int H, int P, void* stream);
 /* Parallel-branch residual step with a grouped RMS norm: x[t] += y1[t] + y2[t] (fp32 rows of pitch ld1 / ld2; y2 or both may be
@@ -461,6 +475,27 @@ int b200_poly_norm(const float* in, int ld, int col0, int n, const float* coef, 
  * out[t][h] = o / sqrt(mean_P(o^2) + eps) * post * sigmoid(gate[t * ldg + gate_col0 + h]) (gate NULL: no gate). */
 int b200_diff_head_norm_gate(const float* a, float lambda, float post, const float* gate, int ldg, int gate_col0, float eps,
                              void* out, int out_dtype, int T, int H, int rep, int P, void* stream);
+/* ---------------------------------------------------------------- dual-norm parallel decoders (window + pooled-block attention
+ * beside a gated linear recurrence)
+ * x[t] = e / sqrt(mean(e^2) + eps) * w, e = table[token]: out fp32 [T][W] */
+int b200_embed_rmsnorm(const int32_t* tokens, const void* table, int table_dtype, const float* w, float eps, float* out, int T,
+                       int W, int V, void* stream);
+/* x[t] += c1 y1[t] + c2 y2[t] + c3 sum_{k < nsum} y3_weight[t][k] y3[t nsum + k] + add_rows[t] + add_vec (fp32; y1 / y2 rows of
+ * pitch ld1 / ld2, y3 [T nsum][W], add_rows [T][W], add_vec [W]; every term may be NULL, y3_weight NULL: plain sum), then
+ * out1[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w1 and out2[t] = the same times w2, in out_dtype (either may be NULL). */
+int b200_scaled_add_rmsnorm2(float* x, const float* y1, int ld1, float c1, const float* y2, int ld2, float c2, const float* y3,
+                             int nsum, const float* y3_weight, float c3, const float* add_rows, const float* add_vec,
+                             const float* w1, void* out1, const float* w2, void* out2, float eps, int out_dtype, int T, int W,
+                             void* stream);
+/* Gated linear recurrence, preparation, IN PLACE on the fp32 rows proj (pitch ld): columns [q_col0, q_col0 + n) become silu(z),
+ * columns [f_col0, f_col0 + n) become lower + (1 - lower) sigmoid(z + f_bias); f_bias, lower fp32 [n]. */
+int b200_gated_scan_prep(float* proj, int ld, int q_col0, int f_col0, int n, const float* f_bias, const float* lower, int T,
+                         void* stream);
+/* Gated linear recurrence over a ragged batch: per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q, f [H][D]
+ * and v [H][P] the columns q_col0 / f_col0 / v_col0 of the fp32 rows proj.  state fp32 [slots][H][P][D] (transposed), read for
+ * sequences with seq_pos0 > 0 and written back for all; out fp32 [T][H * P].  D <= 256, else B200_ERR_UNSUPPORTED. */
+int b200_gated_scan(const float* proj, int ld, int q_col0, int f_col0, int v_col0, float* state, const int32_t* seq_start,
+                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int D, int P, void* stream);
 /* gate_up fp32 [T][2 ff] (gate first): out = act(gate) * up, act = B200_ACT_SILU or B200_ACT_GELU_TANH */
 int b200_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, int act, void* stream);
 /* Gated delta rule, preparation: qkv fp32 rows [q: G*D | k: G*D | v: H*P] (pitch ldc) are the convolved activations; q and k

@@ -12,10 +12,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200_paged.so")
 
 OK = 0
-ABI_VERSION = 11
+ABI_VERSION = 12
 BF16, FP8_E4M3, INT8, F32 = 0, 1, 2, 3
 ACT_SWISH_CLAMPED, ACT_SILU, ACT_GELU_TANH = 0, 1, 2   # gate activation of a gated-linear unit
-ROUTE_SIGMOID, ROUTE_SOFTMAX_TOP = 0, 1                # router weights: sigmoid of each chosen logit | softmax over the chosen
+ROUTE_SIGMOID, ROUTE_SOFTMAX_TOP, ROUTE_SOFTMAX_RENORM = 0, 1, 2   # router weights: sigmoid of each chosen logit | softmax over
+# the chosen | softmax over all experts, the chosen scores divided by their sum
 
 _p = C.c_void_p
 _i = C.c_int
@@ -80,17 +81,18 @@ SIGNATURES = {
     "b200_kv_write_vmix": (_i, [_p, _i, _i, _i, _p, _f, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "b200_causal_conv": (_i, [_p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "b200_swa_sink_attn": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _i,
-                                _i, _p, _p]),
+                                _i, _p, _p, _p, _i, _p]),
+    "b200_kv_pool_mean": (_i, [_p, _p, _p, _p, _i, _p, _i64, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _f,
-                                        _p, _i, _i, _i, _p]),
+                                        _p, _i, _i, _i, _p, _p, _i, _p]),
     "b200_swa_sink_attn_prefill_tc_supported": (_i, [_i, _i, _i, _i, _i, _i]),
     "b200_swa_sink_attn_prefill_tc": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _i, _i, _f, _p, _i, _i, _i, _i, _i, _i, _f, _p, _i,
                                            _i, _i, _p]),
     "b200_swa_sink_attn_decode_tc": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i,
-                                          _i, _i, _i, _p, _p]),
+                                          _i, _i, _i, _p, _p, _p, _i, _p]),
     "b200_attn_split_merge": (_i, [_p, _i, _i, _i, _i, _i, _p, _i64, _p]),
     "b200_qk_norm_rope_kv_write": (_i, [_p, _i, _i, _i, _i, _p, _p, _f, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i,
-                                        _i, _i, _p]),
+                                        _i, _i, _p, _p]),
     "b200_moe_topk": (_i, [_p, _i, _p, _i, _p, _p, _i, _i, _i, _p]),
     "b200_moe_tile_rows": (_i, []),
     "b200_moe_gather_scale": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _p, _i, _p]),
@@ -107,6 +109,11 @@ SIGNATURES = {
     "b200_add_group_rmsnorm": (_i, [_p, _p, _i, _p, _i, _p, _i, _f, _p, _i, _i, _i, _p]),
     "b200_poly_norm": (_i, [_p, _i, _i, _i, _p, _f, _p, _i, _i, _i, _p]),
     "b200_diff_head_norm_gate": (_i, [_p, _f, _f, _p, _i, _i, _f, _p, _i, _i, _i, _i, _i, _p]),
+    # dual-norm parallel decoders: normed embedding, scaled residual step with two norms, gated linear recurrence
+    "b200_embed_rmsnorm": (_i, [_p, _p, _i, _p, _f, _p, _i, _i, _i, _p]),
+    "b200_scaled_add_rmsnorm2": (_i, [_p, _p, _i, _f, _p, _i, _f, _p, _i, _p, _f, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _p]),
+    "b200_gated_scan_prep": (_i, [_p, _i, _i, _i, _i, _p, _p, _i, _p]),
+    "b200_gated_scan": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "b200_delta_prep": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p]),
     "b200_delta_scan": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "b200_latent_kv_write": (_i, [_p, _i, _i, _i, _i, _i, _p, _f, _p, _p, _p, _p, _p, _i, _i, _p]),

@@ -13,7 +13,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200_paged.so")
 SOURCES = ["host.cu", "kv_ops.cu", "paged_attn.cu", "paged_attn_prefill_tc.cu", "gemm_tcgen05.cu", "tp_allreduce.cu", "sampling.cu",
            "dyt_norm.cu", "ssm_scan.cu", "swa_attn.cu", "swa_attn_prefill.cu", "swa_attn_prefill_tc.cu", "moe.cu", "rms_norm.cu", "delta_rule.cu",
-           "latent_attn.cu"]
+           "latent_attn.cu", "gated_scan.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "hybrid_common.cuh"), os.path.join(os.path.dirname(HERE), "include", "b200_paged.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -21,7 +21,8 @@ constexpr int GL_BK = 16;
 constexpr int GL_THREADS = 256;
 
 // one thread per token: the `top` largest logits (+ bias; ties to the lower index); weight = sigmoid(logit), or the softmax
-// over the chosen logits (mode B200_ROUTE_SOFTMAX_TOP)
+// over the chosen logits (mode B200_ROUTE_SOFTMAX_TOP), or the softmax over all experts renormalised over the chosen
+// (B200_ROUTE_SOFTMAX_RENORM)
 __global__ void moe_topk_kernel(const float* __restrict__ z, int ld, const float* __restrict__ bias, int mode, int E, int top,
                                 int32_t* __restrict__ idx, float* __restrict__ wt, int ntok) {
   griddep_launch();
@@ -46,7 +47,17 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, int ld, const float
     out[c] = bi;
     w[c] = best;
   }
-  if (mode == B200_ROUTE_SOFTMAX_TOP) {
+  if (mode == B200_ROUTE_SOFTMAX_RENORM) {
+    // scores = softmax over ALL experts; the chosen scores are divided by their own sum (+ 1e-20)
+    const float m = w[0];
+    float all = 0.f, sum = 0.f;
+    for (int e = 0; e < E; ++e) all += expf(zr[e] + (bias ? bias[e] : 0.f) - m);
+    for (int c = 0; c < top; ++c) {
+      w[c] = expf(w[c] - m) / all;
+      sum += w[c];
+    }
+    for (int c = 0; c < top; ++c) w[c] = w[c] / (sum + 1e-20f);
+  } else if (mode == B200_ROUTE_SOFTMAX_TOP) {
     const float m = w[0];  // the first chosen is the largest
     float sum = 0.f;
     for (int c = 0; c < top; ++c) sum += expf(w[c] - m);
@@ -537,7 +548,8 @@ int b200_moe_topk(const float* logits, int ld, const float* bias, int mode, int3
                   int top, void* stream) {
   B200_REQUIRE(logits && topk_idx && topk_weight, "moe_topk: null pointer");
   B200_REQUIRE(E >= 1 && top >= 1 && top <= E && ld >= E, "moe_topk: top %d of %d experts", top, E);
-  B200_REQUIRE(mode == B200_ROUTE_SIGMOID || mode == B200_ROUTE_SOFTMAX_TOP, "moe_topk: routing mode %d", mode);
+  B200_REQUIRE(mode == B200_ROUTE_SIGMOID || mode == B200_ROUTE_SOFTMAX_TOP || mode == B200_ROUTE_SOFTMAX_RENORM,
+               "moe_topk: routing mode %d", mode);
   if (T <= 0) return B200_OK;
   B200_CUDA_OK(launch_kernel(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, (cudaStream_t)stream, logits, ld, bias, mode, E,
                              top, topk_idx, topk_weight, T));

@@ -109,6 +109,7 @@ __global__ void rmsnorm_cols_kernel(const float* __restrict__ in, int ld, int co
 }
 
 // One warp per (token, head): out = o / sqrt(mean_P(o^2) + eps) * w[0..P) * silu(gate), gate = columns of the fp32 rows gate_src
+// (gate NULL: no gate)
 template <typename OT>
 __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ldg, int gcol0,
                                          const float* __restrict__ w, float eps, OT* __restrict__ out, int T, int H, int P) {
@@ -124,6 +125,10 @@ __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const floa
   for (int i = lane; i < P; i += 32) ss += r[i] * r[i];
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)P + eps);
+  if (!gate) {  // no output gate: the norm alone
+    for (int i = lane; i < P; i += 32) stf(out, wid * P + i, r[i] * inv * w[i]);
+    return;
+  }
   const float* gr = gate + t * ldg + gcol0 + (int64_t)h * P;
   for (int i = lane; i < P; i += 32) stf(out, wid * P + i, r[i] * inv * w[i] * silu_f(gr[i]));
 }
@@ -272,6 +277,73 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 }
 
 // gu [T, 2 ff] (gate columns first): out = act(g) * u
+// x[t] = e / sqrt(mean(e^2) + eps) * w with e = table[token]: a token embedding that is normed before it enters the stream
+template <typename WT>
+__global__ void embed_rmsnorm_kernel(const int32_t* __restrict__ tokens, const WT* __restrict__ table, const float* __restrict__ w,
+                                     float eps, float* __restrict__ out, int W, int V) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = ldf(table, (int64_t)tok * W + i);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) out[(int64_t)t * W + i] = ldf(table, (int64_t)tok * W + i) * inv * w[i];
+}
+
+// Residual step of layers whose branches are scaled sums read through TWO norms of the same stream:
+//   x[t] += c1 y1[t] + c2 y2[t] + c3 sum_{k < nsum} wt[t][k] y3[t nsum + k] + add_rows[t] + add_vec     (every term optional)
+//   out1[t] = x[t] / rms(x[t]) * w1,  out2[t] = x[t] / rms(x[t]) * w2                                    (either may be absent)
+// One CTA per token, the row in shared memory, one sum of squares for both norms.
+template <typename OT>
+__global__ void scaled_add_rmsnorm2_kernel(float* __restrict__ x, const float* __restrict__ y1, int ld1, float c1,
+                                           const float* __restrict__ y2, int ld2, float c2, const float* __restrict__ y3, int nsum,
+                                           const float* __restrict__ wt, float c3, const float* __restrict__ add_rows,
+                                           const float* __restrict__ add_vec, const float* __restrict__ w1, OT* __restrict__ out1,
+                                           const float* __restrict__ w2, OT* __restrict__ out2, float eps, int W) {
+  griddep_launch();
+  griddep_wait();
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const bool touched = y1 || y2 || y3 || add_rows || add_vec;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float r = x[(int64_t)t * W + i];
+    float b = 0.f;
+    if (y1) b += c1 * y1[(int64_t)t * ld1 + i];
+    if (y2) b += c2 * y2[(int64_t)t * ld2 + i];
+    if (y3) {
+      float s = 0.f;
+      for (int c = 0; c < nsum; ++c) {
+        const float v = y3[((int64_t)t * nsum + c) * W + i];
+        s += wt ? wt[(int64_t)t * nsum + c] * v : v;
+      }
+      b += c3 * s;
+    }
+    r += b;
+    if (add_rows) r += add_rows[(int64_t)t * W + i];
+    if (add_vec) r += add_vec[i];
+    row[i] = r;
+    ss += r * r;
+    if (touched) x[(int64_t)t * W + i] = r;
+  }
+  if (!out1 && !out2) return;
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float u = row[i] * inv;
+    if (out1) stf(out1, (int64_t)t * W + i, u * w1[i]);
+    if (out2) stf(out2, (int64_t)t * W + i, u * w2[i]);
+  }
+}
+
 template <typename OT>
 __global__ void glu_kernel(const float* __restrict__ gu, OT* __restrict__ out, int ff, int act, int64_t total) {
   griddep_launch();
@@ -331,12 +403,40 @@ int b200_rmsnorm_cols(const float* in, int ld, int col0, int n, const float* w, 
 
 int b200_head_rmsnorm_gate(const float* o, const float* gate, int ldg, int gate_col0, const float* w, float eps, void* out,
                            int out_dtype, int T, int H, int P, void* stream) {
-  B200_REQUIRE(o && gate && w && out && H >= 1 && P >= 1, "head_rmsnorm_gate: null pointer or bad shape");
+  B200_REQUIRE(o && w && out && H >= 1 && P >= 1, "head_rmsnorm_gate: null pointer or bad shape");
   if (T <= 0) return B200_OK;
   const int64_t warps = (int64_t)T * H;
   B200_DISPATCH_ELEM(out_dtype, OT,
                      B200_CUDA_OK(launch_kernel(head_rmsnorm_gate_kernel<OT>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0,
                                                 (cudaStream_t)stream, o, gate, ldg, gate_col0, w, eps, (OT*)out, T, H, P)));
+  return B200_OK;
+}
+
+int b200_embed_rmsnorm(const int32_t* tokens, const void* table, int table_dtype, const float* w, float eps, float* out, int T,
+                       int W, int V, void* stream) {
+  B200_REQUIRE(tokens && table && w && out && W >= 1 && V >= 1, "embed_rmsnorm: null pointer or bad shape");
+  if (T <= 0) return B200_OK;
+  B200_DISPATCH_ELEM(table_dtype, WT,
+                     B200_CUDA_OK(launch_kernel(embed_rmsnorm_kernel<WT>, dim3(T), dim3(W >= 1024 ? 256 : 128), 0,
+                                                (cudaStream_t)stream, tokens, (const WT*)table, w, eps, out, W, V)));
+  return B200_OK;
+}
+
+int b200_scaled_add_rmsnorm2(float* x, const float* y1, int ld1, float c1, const float* y2, int ld2, float c2, const float* y3,
+                             int nsum, const float* y3_weight, float c3, const float* add_rows, const float* add_vec,
+                             const float* w1, void* out1, const float* w2, void* out2, float eps, int out_dtype, int T, int W,
+                             void* stream) {
+  B200_REQUIRE(x && (!out1 || w1) && (!out2 || w2) && (!y3 || nsum >= 1), "scaled_add_rmsnorm2: null pointer");
+  B200_REQUIRE((size_t)W * 4 <= 200 * 1024, "scaled_add_rmsnorm2: rows of %d do not fit shared memory", W);
+  if (T <= 0) return B200_OK;
+  const size_t smem = (size_t)W * 4;
+  B200_DISPATCH_ELEM(out_dtype, OT, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(scaled_add_rmsnorm2_kernel<OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_OK(launch_kernel(scaled_add_rmsnorm2_kernel<OT>, dim3(T), dim3(W >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, x,
+                               y1, ld1, c1, y2, ld2, c2, y3, nsum, y3_weight, c3, add_rows, add_vec, w1, (OT*)out1, w2, (OT*)out2,
+                               eps, W));
+  });
   return B200_OK;
 }
 

@@ -59,7 +59,8 @@ __global__ void qk_norm_rope_kv_write_kernel(const float* __restrict__ src, int 
                                              int rot_n, int rot_half, const float* __restrict__ cos_t,
                                              const float* __restrict__ sin_t, const int32_t* __restrict__ tok_pos,
                                              const int64_t* __restrict__ slots, float* __restrict__ q_out, KT* __restrict__ k_pool,
-                                             KT* __restrict__ v_pool, int H, int G, int Gv, int D, int Dv, int bs) {
+                                             KT* __restrict__ v_pool, int H, int G, int Gv, int D, int Dv, int bs,
+                                             const float* __restrict__ q_head_scale) {
   griddep_launch();
   griddep_wait();
   __shared__ float red[2][33];
@@ -119,7 +120,8 @@ __global__ void qk_norm_rope_kv_write_kernel(const float* __restrict__ src, int 
     const float o = row[col0 + partner] * (nw ? inv * nw[partner] : 1.0f);
     return first ? u * cs[idx] - o * sn[idx] : u * cs[idx] + o * sn[idx];
   };
-  for (int i = threadIdx.x; i < nq; i += blockDim.x) q_out[(int64_t)t * nq + i] = turned(q_col0, q_norm, inv_q, i);
+  for (int i = threadIdx.x; i < nq; i += blockDim.x)
+    q_out[(int64_t)t * nq + i] = turned(q_col0, q_norm, inv_q, i) * (q_head_scale ? q_head_scale[i / D] : 1.0f);
   if (slot < 0) return;
   for (int i = threadIdx.x; i < nk; i += blockDim.x) {
     const int g = i / D, d = i - g * D;
@@ -141,7 +143,7 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const float* __restrict__ src, 
                                                  const float* __restrict__ sin_t, const int32_t* __restrict__ tok_pos,
                                                  const int64_t* __restrict__ slots, float* __restrict__ q_out,
                                                  KT* __restrict__ k_pool, KT* __restrict__ v_pool, int H, int G, int Gv, int D, int Dv,
-                                                 int bs) {
+                                                 int bs, const float* __restrict__ q_head_scale) {
   griddep_launch();
   griddep_wait();
   __shared__ float red[2][33];
@@ -220,8 +222,14 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const float* __restrict__ src, 
       *reinterpret_cast<float4*>(p) = v;
     }
   };
-  for (int i = threadIdx.x * 4; i < nq; i += blockDim.x * 4)
-    *reinterpret_cast<float4*>(q_out + (int64_t)t * nq + i) = turned(q_col0, q_norm, inv_q, i, i % D);
+  for (int i = threadIdx.x * 4; i < nq; i += blockDim.x * 4) {
+    float4 r = turned(q_col0, q_norm, inv_q, i, i % D);
+    if (q_head_scale) {  // D % 4 == 0: the four columns belong to one head
+      const float hs = q_head_scale[i / D];
+      r.x *= hs, r.y *= hs, r.z *= hs, r.w *= hs;
+    }
+    *reinterpret_cast<float4*>(q_out + (int64_t)t * nq + i) = r;
+  }
   if (slot < 0) return;
   for (int i = threadIdx.x * 4; i < nk; i += blockDim.x * 4) {
     const int g = i / D, d = i - g * D;
@@ -230,6 +238,38 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const float* __restrict__ src, 
   for (int i = threadIdx.x * 4; i < Gv * Dv; i += blockDim.x * 4) {
     const int g = i / Dv, d = i - g * Dv;
     put(v_pool + ((blk * Gv + g) * bs + off) * Dv + d, ld4(row + v_col0 + i));
+  }
+}
+
+// Block means for attention that sees far-away blocks of `pool` positions as one key / value each.  One CTA per token of the
+// step; the CTA of a token that CLOSES a block (position = b pool + pool - 1) reads the block's `pool` key and value rows back
+// from the pools through the sequence's block table (rows of earlier steps and of this one alike: what is averaged is what
+// the cache holds), sums them in fp32, divides by `pool` and writes the mean into the pooled pools
+// PK [num_blocks][G][ppb][D], PV [num_blocks][Gv][ppb][Dv], ppb = ceil(block_size / pool): the entry of block b lives in the page
+// that holds the block's last position e, at index (e % block_size) / pool.  Runs after the step's keys and values are written.
+template <typename KT>
+__global__ void kv_pool_mean_kernel(const KT* __restrict__ k_pool, const KT* __restrict__ v_pool, KT* __restrict__ pk_pool,
+                                    KT* __restrict__ pv_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
+                                    const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos,
+                                    const int64_t* __restrict__ slots, int G, int Gv, int D, int Dv, int bs, int pool, int ppb) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  if (slots[t] < 0 || (pos + 1) % pool != 0) return;
+  const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
+  const int first = pos - pool + 1;
+  const int64_t dst_blk = bt[pos / bs];
+  const int dst_idx = (pos % bs) / pool;
+  const float inv = 1.0f / (float)pool;
+  for (int i = threadIdx.x; i < G * D + Gv * Dv; i += blockDim.x) {
+    const bool key = i < G * D;
+    const int c = key ? i : i - G * D, W = key ? D : Dv, N = key ? G : Gv;
+    const int g = c / W, d = c - g * W;
+    const KT* src = key ? k_pool : v_pool;
+    float s = 0.f;
+    for (int p = first; p <= pos; ++p) s += ldf(src, (((int64_t)bt[p / bs] * N + g) * bs + p % bs) * W + d);
+    stf(key ? pk_pool : pv_pool, ((dst_blk * N + g) * ppb + dst_idx) * W + d, s * inv);
   }
 }
 
@@ -318,7 +358,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                          const int32_t* __restrict__ block_table, int64_t bt_stride, const int32_t* __restrict__ tok_row,
                          const int32_t* __restrict__ tok_pos, const float* __restrict__ sink, float scale, int window,
                          void* __restrict__ out, int T, int H, int G, int D, int Dv, int bs, int v_pitch, int chunk, float softcap,
-                         const float* __restrict__ sig_bias, int v_div, int out_f32, float* __restrict__ part) {
+                         const float* __restrict__ sig_bias, int v_div, int out_f32, float* __restrict__ part,
+                         const KT* __restrict__ pk_pool, const KT* __restrict__ pv_pool, int pool, int ppb) {
   griddep_launch();
   griddep_wait();
   extern __shared__ __align__(16) float sm_att[];
@@ -354,18 +395,31 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) acc[qh][c] = make_float2(0.f, 0.f);
   }
-  for (int j0 = lo + 32 * (warp + ATT_WARPS * split); j0 <= pos; j0 += 32 * ATT_WARPS * splits) {
-    const int j = j0 + lane;
-    const bool valid = j <= pos;
-    int64_t tile = 0, vtile = 0;  // row index of (block, kv head, token) in the key / value pool
+  // pooled blocks: block b (positions b pool .. b pool + pool - 1) is seen as one key / value once it lies wholly before the
+  // window, b pool + pool - 1 <= pos - window; its row sits in the page of its last position.  The tile list is the pooled
+  // entries (32 per tile) followed by the window's keys.
+  const int nb = pool > 0 && pos - window + 1 > 0 ? (pos - window + 1) / pool : 0;
+  const int npt = (nb + 31) >> 5, ntt = ((pos - lo) >> 5) + 1;
+  for (int ti = warp + ATT_WARPS * split; ti < npt + ntt; ti += ATT_WARPS * splits) {
+    const bool pooled = ti < npt;
+    const int j = pooled ? ti * 32 + lane : lo + (ti - npt) * 32 + lane;  // pooled block, or key position
+    const bool valid = pooled ? j < nb : j <= pos;
+    const KT* vrow = v_pool;  // lanes past the last key: row 0 of the pool (the null page, finite values) with weight 0
     float p[QH];
 #pragma unroll
     for (int qh = 0; qh < QH; ++qh) p[qh] = 0.f;
     if (valid) {
-      const int64_t blk = bt[j / bs];
-      tile = (blk * G + g) * bs + (j % bs);
-      vtile = (blk * Gv + gv) * bs + (j % bs);
-      DotRows<KT, QH>::run(qs, Dp, k_pool + tile * D, D, p);
+      if (pooled) {
+        const int e = j * pool + pool - 1;
+        const int64_t blk = bt[e / bs];
+        const int idx = (e % bs) / pool;
+        vrow = pv_pool + ((blk * Gv + gv) * ppb + idx) * (int64_t)Dv;
+        DotRows<KT, QH>::run(qs, Dp, pk_pool + ((blk * G + g) * ppb + idx) * (int64_t)D, D, p);
+      } else {
+        const int64_t blk = bt[j / bs];
+        vrow = v_pool + ((blk * Gv + gv) * bs + (j % bs)) * (int64_t)v_pitch;
+        DotRows<KT, QH>::run(qs, Dp, k_pool + ((blk * G + g) * bs + (j % bs)) * (int64_t)D, D, p);
+      }
     }
 #pragma unroll
     for (int qh = 0; qh < QH; ++qh) {
@@ -391,11 +445,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     // null page: finite values), so they add nothing
 #pragma unroll 8
     for (int jj = 0; jj < 32; ++jj) {
-      const int64_t tj = __shfl_sync(0xffffffffu, vtile, jj);
+      const KT* vr = reinterpret_cast<const KT*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(vrow), jj));
       float pj[QH];
 #pragma unroll
       for (int qh = 0; qh < QH; ++qh) pj[qh] = __shfl_sync(0xffffffffu, p[qh], jj);
-      const KT* vr = v_pool + tj * v_pitch;
 #pragma unroll
       for (int c = 0; c < MAXC; ++c) {
         const int d = 2 * lane + 64 * c;
@@ -505,7 +558,7 @@ int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0,
                                const float* k_norm, float eps, int rot_n, int rot_half, const float* cos_table,
                                const float* sin_table, const int32_t* tok_pos, const int64_t* slot_mapping, float* q_out,
                                void* k_pool, void* v_pool, int kv_dtype, int T, int H, int G, int Gv, int D, int Dv, int block_size,
-                               void* stream) {
+                               const float* q_head_scale, void* stream) {
   B200_REQUIRE(src && tok_pos && slot_mapping && q_out && k_pool && v_pool, "qk_norm_rope_kv_write: null pointer");
   B200_REQUIRE(rot_n >= 0 && rot_n <= D && rot_n % 2 == 0 && (rot_n == 0 || (cos_table && sin_table)),
                "qk_norm_rope_kv_write: %d rotating columns in heads of %d", rot_n, D);
@@ -522,13 +575,28 @@ int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0,
                        B200_CUDA_OK(launch_kernel(qk_norm_rope_kv_write_vec_kernel<KT>, dim3(T), dim3(threads), 0, (cudaStream_t)stream,
                                                   src, ld, q_col0, k_col0, v_col0, q_norm, k_norm, eps, rot_n, rot_half, cos_table,
                                                   sin_table, tok_pos, slot_mapping, q_out, (KT*)k_pool, (KT*)v_pool, H, G, Gv, D, Dv,
-                                                  block_size)));
+                                                  block_size, q_head_scale)));
     return B200_OK;
   }
   B200_DISPATCH_ELEM(kv_dtype, KT,
                      B200_CUDA_OK(launch_kernel(qk_norm_rope_kv_write_kernel<KT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, src, ld,
                                                 q_col0, k_col0, v_col0, q_norm, k_norm, eps, rot_n, rot_half, cos_table, sin_table,
-                                                tok_pos, slot_mapping, q_out, (KT*)k_pool, (KT*)v_pool, H, G, Gv, D, Dv, block_size)));
+                                                tok_pos, slot_mapping, q_out, (KT*)k_pool, (KT*)v_pool, H, G, Gv, D, Dv, block_size,
+                                                q_head_scale)));
+  return B200_OK;
+}
+
+int b200_kv_pool_mean(const void* k_pool, const void* v_pool, void* pooled_k, void* pooled_v, int kv_dtype,
+                      const int32_t* block_table, int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos,
+                      const int64_t* slot_mapping, int T, int G, int Gv, int D, int Dv, int block_size, int pool, void* stream) {
+  B200_REQUIRE(k_pool && v_pool && pooled_k && pooled_v && block_table && tok_row && tok_pos && slot_mapping, "kv_pool_mean: null pointer");
+  B200_REQUIRE(pool >= 1 && G >= 1 && Gv >= 1 && D >= 1 && Dv >= 1 && block_size >= 1, "kv_pool_mean: blocks of %d positions", pool);
+  if (T <= 0) return B200_OK;
+  const int ppb = (block_size + pool - 1) / pool;
+  B200_DISPATCH_ELEM(kv_dtype, KT,
+                     B200_CUDA_OK(launch_kernel(kv_pool_mean_kernel<KT>, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const KT*)k_pool,
+                                                (const KT*)v_pool, (KT*)pooled_k, (KT*)pooled_v, block_table, bt_stride, tok_row,
+                                                tok_pos, slot_mapping, G, Gv, D, Dv, block_size, pool, ppb)));
   return B200_OK;
 }
 
@@ -536,8 +604,10 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
                        int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
                        float softcap, const float* sigmoid_bias, int v_div, int out_f32, int splits, float* split_workspace,
-                       void* stream) {
+                       const void* pooled_k, const void* pooled_v, int pool, void* stream) {
   B200_REQUIRE(q && k_pool && v_pool && block_table && tok_row && tok_pos && out, "swa_sink_attn: null pointer");
+  B200_REQUIRE(pool >= 0 && (pool == 0 || (pooled_k && pooled_v && v_pool != k_pool)), "swa_sink_attn: blocks of %d need pooled pools", pool);
+  const int ppb = pool > 0 ? (block_size + pool - 1) / pool : 0;
   B200_REQUIRE(v_pitch >= Dv, "swa_sink_attn: value rows of pitch %d hold %d values", v_pitch, Dv);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "swa_sink_attn: %d query heads over %d kv heads", H, G);
   B200_REQUIRE(window >= 1 && chunk >= 0, "swa_sink_attn: window %d, chunk %d", window, chunk);
@@ -563,7 +633,7 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
     B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC, QH>, grid, dim3(ATT_WARPS * 32), smem, st, q, ldq,               \
                                (const KT*)k_pool, (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, \
                                window, out, T, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32,       \
-                               split_workspace));                                                                           \
+                               split_workspace, (const KT*)pooled_k, (const KT*)pooled_v, pool, ppb));                      \
   } while (0)
 #define ATT_LAUNCH(MC)                \
   do {                                \

@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(PF_THREADS, DV16M <= 8 ? 512 / PF_THREADS : 25
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                             const int32_t* __restrict__ seq_pos0, const float* __restrict__ sink, float scale, int window,
                             void* __restrict__ out, int H, int G, int D, int Dv, int bs, int v_pitch, int chunk, float softcap,
-                            const float* __restrict__ sig_bias, int v_div, int out_f32, int split_p, int bs_shift) {
+                            const float* __restrict__ sig_bias, int v_div, int out_f32, int split_p, int bs_shift,
+                            const __nv_bfloat16* __restrict__ pk_pool, const __nv_bfloat16* __restrict__ pv_pool, int pool, int ppb) {
   griddep_wait();
   // the last rows of a portion see the most keys: their tiles are launched first, so the longest CTAs do not form the tail
   const int sq = blockIdx.z, h = blockIdx.y, i0 = (gridDim.x - 1 - blockIdx.x) * PF_ROWS;
@@ -90,34 +91,61 @@ __global__ void __launch_bounds__(PF_THREADS, DV16M <= 8 ? 512 / PF_THREADS : 25
   // Four threads share a row and take its 16-byte chunks in turn, so the page look-up happens once per thread and tile.
   constexpr int TPR = PF_THREADS / PF_KEYS;
   const int ir = tid / TPR, ic = tid % TPR;
-  // the page of this thread's row in the tile at j0 (looked up one tile before the copies that need it are issued)
-  auto page_of = [&](int j0) -> int64_t {
-    const int j = j0 + ir;
-    if (j > j_hi) return 0;
+  // Pooled blocks (pool > 0): block b of `pool` positions is one key / value for the rows that have it wholly before their
+  // window, b pool + pool - 1 <= position - window; its row sits in the pooled pools, in the page of the block's last position.
+  // The CTA's tile list is the pooled entries its LAST row sees (32 per tile), then the key positions as before; tile `it`
+  // of the list is pooled while it < npt.
+  const int nb_max = pool > 0 && j_hi - window + 1 > 0 ? (j_hi - window + 1) / pool : 0;
+  const int npt = (nb_max + PF_KEYS - 1) / PF_KEYS;
+  const int j_first = (j_lo / PF_KEYS) * PF_KEYS;
+  const int ntiles = npt + (j_hi - j_first) / PF_KEYS + 1;
+  // the page of this thread's row in tile `it` (looked up one tile before the copies that need it are issued)
+  auto page_of = [&](int it) -> int64_t {
+    if (it < npt) {
+      const int b = it * PF_KEYS + ir;
+      if (b >= nb_max) return 0;
+      const int e = b * pool + pool - 1;
+      return bt[bs_shift >= 0 ? e >> bs_shift : e / bs];
+    }
+    const int j = j_first + (it - npt) * PF_KEYS + ir;
+    if (it >= ntiles || j > j_hi) return 0;
     return bt[bs_shift >= 0 ? j >> bs_shift : j / bs];
   };
-  auto issue = [&](int j0, int st, int64_t blk) {
-    if (j0 <= j_hi) {
-      const int j = j0 + ir;
-      const bool ok = j <= j_hi;
-      const int off = ok ? (bs_shift >= 0 ? j & (bs - 1) : j % bs) : 0;
-      const __nv_bfloat16* kr = k_pool + ((blk * G + g) * bs + off) * D;
-      const __nv_bfloat16* vr = v_pool + ((blk * Gv + gv) * bs + off) * v_pitch;
+  auto issue = [&](int it, int st, int64_t blk) {
+    if (it < ntiles) {
+      const __nv_bfloat16 *kr, *vr;
+      bool ok;
+      if (it < npt) {
+        const int b = it * PF_KEYS + ir;
+        ok = b < nb_max;
+        const int e = b * pool + pool - 1;
+        const int idx = ok ? (bs_shift >= 0 ? e & (bs - 1) : e % bs) / pool : 0;
+        kr = pk_pool + ((blk * G + g) * ppb + idx) * D;
+        vr = pv_pool + ((blk * Gv + gv) * ppb + idx) * Dv;
+      } else {
+        const int j = j_first + (it - npt) * PF_KEYS + ir;
+        ok = j <= j_hi;
+        const int off = ok ? (bs_shift >= 0 ? j & (bs - 1) : j % bs) : 0;
+        kr = k_pool + ((blk * G + g) * bs + off) * D;
+        vr = v_pool + ((blk * Gv + gv) * bs + off) * v_pitch;
+      }
       const uint32_t kd = smem_u32(Ks0 + (st * PF_KEYS + ir) * ldk), vd = smem_u32(Vs0 + (st * PF_KEYS + ir) * ldv);
       for (int c = ic; c < kch; c += TPR) cp_async16(kd + c * 16, kr + c * 8, ok);
       for (int c = ic; c < vch; c += TPR) cp_async16(vd + c * 16, vr + c * 8, ok);
     }
     cp_async_commit();  // an empty group past the last tile keeps the wait counts uniform
   };
-  const int j_first = (j_lo / PF_KEYS) * PF_KEYS;
   static_assert(PF_STAGES == 2, "the page look-ahead below is written for two stages");
-  issue(j_first, 0, page_of(j_first));
-  int64_t blk_next = page_of(j_first + PF_KEYS);
-  for (int j0 = j_first, it = 0; j0 <= j_hi; j0 += PF_KEYS, ++it) {
+  issue(0, 0, page_of(0));
+  int64_t blk_next = page_of(1);
+  for (int it = 0; it < ntiles; ++it) {
     const int st = it % PF_STAGES;
+    const bool ptile = it < npt;
+    // first key position of a window tile, first pooled block of a pooled tile
+    const int j0 = ptile ? it * PF_KEYS : j_first + (it - npt) * PF_KEYS;
     // refill the stage that the barrier at the end of the previous tile released, then wait for this tile's group
-    issue(j0 + PF_KEYS, (it + 1) % PF_STAGES, blk_next);
-    blk_next = page_of(j0 + 2 * PF_KEYS);
+    issue(it + 1, (it + 1) % PF_STAGES, blk_next);
+    blk_next = page_of(it + 2);
     cp_async_wait<PF_STAGES - 1>();
     __syncthreads();  // this tile's copies of every thread have landed (and, first time, Q is written)
     const __nv_bfloat16* Ks = Ks0 + st * PF_KEYS * ldk;
@@ -144,7 +172,8 @@ __global__ void __launch_bounds__(PF_THREADS, DV16M <= 8 ? 512 / PF_THREADS : 25
     // ---- mask, online softmax (fp32).  A tile that every row of the warp sees whole (all its keys at or before the warp's
     // first row, none before the lower bound of its last row; the bounds grow with the position) skips the per-element mask
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
-    const bool whole = j0 + PF_KEYS - 1 <= w_first && j0 >= w_lb;
+    // (a pooled tile: every block of it wholly before the window of the warp's first row)
+    const bool whole = ptile ? (j0 + PF_KEYS) * pool - 1 <= w_first - window : j0 + PF_KEYS - 1 <= w_first && j0 >= w_lb;
     if (whole && !sig && softcap <= 0.f) {
 #pragma unroll
       for (int j = 0; j < PF_NT; ++j) {
@@ -160,7 +189,8 @@ __global__ void __launch_bounds__(PF_THREADS, DV16M <= 8 ? 512 / PF_THREADS : 25
           const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
           const bool hi = c >= 2;
           const int pos = hi ? p_hi : p_lo;
-          const bool seen = whole || ((hi ? ok_hi : ok_lo) && key <= pos && key >= (hi ? lb_hi : lb_lo));
+          const bool seen = whole || ((hi ? ok_hi : ok_lo) && (ptile ? key * pool + pool - 1 <= pos - window
+                                                                            : key <= pos && key >= (hi ? lb_hi : lb_lo)));
           float v = s[j][c] * scale;
           // tanh(x) = 1 - 2 / (1 + e^(2x)): absolute error ~1e-7, so the capped score is good to ~1e-7 of the cap
           if (softcap > 0.f) v = softcap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v * inv_cap)));
@@ -277,7 +307,8 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
                               const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos,
                               const float* __restrict__ sink, float scale, int window, void* __restrict__ out, int H, int G, int D,
                               int Dv, int bs, int v_pitch, int chunk, float softcap, const float* __restrict__ sig_bias, int v_div,
-                              int out_f32, int split_p, float* __restrict__ part) {
+                              int out_f32, int split_p, float* __restrict__ part, const __nv_bfloat16* __restrict__ pk_pool,
+                              const __nv_bfloat16* __restrict__ pv_pool, int pool, int ppb) {
   griddep_wait();
   extern __shared__ __align__(16) unsigned char dt_sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -324,10 +355,11 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   // the 16-byte chunks of a tile row that this lane copies (the same for every row and tile): key chunk c of key head mp comes
   // from that head's row, bs rows after the first head's
   // source offset of a chunk = block * ch_blk + (row of the block) * ch_row + ch_src elements into ch_pool
+  // (pooled blocks, pool > 0: the same chunk of a row of the pooled pools, pages of ppb rows: pc_*)
   bool ch_on[DT_SLOTS];
-  int ch_blk[DT_SLOTS], ch_row[DT_SLOTS], ch_src[DT_SLOTS], ch_pitch[DT_SLOTS];
+  int ch_blk[DT_SLOTS], ch_row[DT_SLOTS], ch_src[DT_SLOTS], ch_pitch[DT_SLOTS], pc_blk[DT_SLOTS], pc_row[DT_SLOTS], pc_src[DT_SLOTS];
   uint32_t ch_dst[DT_SLOTS];
-  const __nv_bfloat16* ch_pool[DT_SLOTS];
+  const __nv_bfloat16 *ch_pool[DT_SLOTS], *pc_pool[DT_SLOTS];
 #pragma unroll
   for (int sl = 0; sl < DT_SLOTS; ++sl) {
     const int c = lane + 32 * sl;
@@ -340,23 +372,42 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     ch_src[sl] = key ? (gv * v_div + mp) * bs * D + (c - mp * kch) * 8 : gv * bs * v_pitch + (c - kcht) * 8;
     ch_pitch[sl] = (key ? ldk : ldv) * 2;
     ch_dst[sl] = key ? smem_u32(Kt) + c * 16 : smem_u32(Vt) + (c - kcht) * 16;
+    pc_row[sl] = key ? D : Dv;
+    pc_blk[sl] = (key ? G : Gv) * ppb * pc_row[sl];
+    pc_pool[sl] = key ? pk_pool : pv_pool;
+    pc_src[sl] = key ? (gv * v_div + mp) * ppb * D + (c - mp * kch) * 8 : gv * ppb * Dv + (c - kcht) * 8;
   }
-  for (int j0 = lo + LDT_KEYS * (warp + DT_WARPS * split); j0 <= pos; j0 += LDT_KEYS * DT_WARPS * splits) {
-    // ---- this warp's 32 key and value rows -> its buffer (rows past the token's position are zeros)
+  // pooled blocks: block b of `pool` positions is one key / value once it lies wholly before the window,
+  // b pool + pool - 1 <= pos - window; the tile list is the pooled entries (32 per tile), then the window's keys
+  const int nb = pool > 0 && pos - window + 1 > 0 ? (pos - window + 1) / pool : 0;
+  const int npt = (nb + LDT_KEYS - 1) / LDT_KEYS, ntt = (pos - lo) / LDT_KEYS + 1;
+  for (int ti = warp + DT_WARPS * split; ti < npt + ntt; ti += DT_WARPS * splits) {
+    // ---- this warp's 32 key and value rows -> its buffer (rows past the token's position / the last seen block are zeros)
+    const bool ptile = ti < npt;
+    const int j0 = ptile ? ti * LDT_KEYS : lo + (ti - npt) * LDT_KEYS;  // first pooled block / first key position of the tile
+    const int j_end = ptile ? nb - 1 : pos;                            // last visible one
     const int jm = j0 + lane;
     int my_blk = -1, my_off = 0;
-    if (jm <= pos) {
-      my_blk = bt[jm / bs];
-      my_off = jm % bs;
+    if (jm <= j_end) {
+      if (ptile) {
+        const int e = jm * pool + pool - 1;
+        my_blk = bt[e / bs];
+        my_off = (e % bs) / pool;
+      } else {
+        my_blk = bt[jm / bs];
+        my_off = jm % bs;
+      }
     }
     for (int r = 0; r < LDT_KEYS; ++r) {
       const int blk = __shfl_sync(0xffffffffu, my_blk, r), off = __shfl_sync(0xffffffffu, my_off, r);
       const bool ok = blk >= 0;
 #pragma unroll
       for (int sl = 0; sl < DT_SLOTS; ++sl) {
-        if (ch_on[sl])
-          cp_async16(ch_dst[sl] + r * ch_pitch[sl],
-                     ch_pool[sl] + ((int64_t)(ok ? blk : 0) * ch_blk[sl] + (off * ch_row[sl] + ch_src[sl])), ok);
+        if (ch_on[sl]) {
+          const __nv_bfloat16* src = ptile ? pc_pool[sl] + ((int64_t)(ok ? blk : 0) * pc_blk[sl] + (off * pc_row[sl] + pc_src[sl]))
+                                           : ch_pool[sl] + ((int64_t)(ok ? blk : 0) * ch_blk[sl] + (off * ch_row[sl] + ch_src[sl]));
+          cp_async16(ch_dst[sl] + r * ch_pitch[sl], src, ok);
+        }
       }
     }
     cp_async_commit();
@@ -388,7 +439,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
-        const bool hi = c >= 2, seen = key <= pos;
+        const bool hi = c >= 2, seen = key <= j_end;
         float v = s[j][c] * scale;
         if (softcap > 0.f) v = softcap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v * inv_cap)));
         if (sig) v = seen ? __fdividef(1.0f, 1.0f + __expf(-(v + (hi ? sb_hi : sb_lo)))) : 0.f;
@@ -518,7 +569,9 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
                                int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
                                int Dv, int v_pitch, int block_size, int chunk, float softcap, const float* sigmoid_bias, int v_div,
-                               int out_f32, int split_p, void* stream) {
+                               int out_f32, int split_p, const void* pooled_k, const void* pooled_v, int pool, void* stream) {
+  B200_REQUIRE(pool >= 0 && (pool == 0 || (pooled_k && pooled_v && v_pool != k_pool)), "swa_sink_attn_prefill: blocks of %d need pooled pools", pool);
+  const int ppb = pool > 0 ? (block_size + pool - 1) / pool : 0;
   B200_REQUIRE(q && k_pool && v_pool && block_table && seq_start && seq_slot && seq_pos0 && out,
                "swa_sink_attn_prefill: null pointer");
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && window >= 1, "swa_sink_attn_prefill: %d query heads over %d kv heads", H, G);
@@ -542,7 +595,8 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
       B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_prefill_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     B200_CUDA_OK(launch_kernel(swa_sink_prefill_kernel<M>, grid, dim3(PF_THREADS), smem, st, q, ldq, (const BT*)k_pool,              \
                                (const BT*)v_pool, block_table, bt_stride, seq_start, seq_slot, seq_pos0, sink, scale, window, \
-                               out, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p, bs_shift)); \
+                               out, H, G, D, Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p, bs_shift, \
+                               (const BT*)pooled_k, (const BT*)pooled_v, pool, ppb));                                         \
   } while (0)
   if (Dv <= 64) PF_LAUNCH(4);
   else if (Dv <= 128) PF_LAUNCH(8);
@@ -555,7 +609,9 @@ int b200_swa_sink_attn_decode_tc(const float* q, int ldq, const void* k_pool, co
                                  int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
                                  int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
                                  float softcap, const float* sigmoid_bias, int v_div, int out_f32, int split_p, int splits,
-                                 float* split_workspace, void* stream) {
+                                 float* split_workspace, const void* pooled_k, const void* pooled_v, int pool, void* stream) {
+  B200_REQUIRE(pool >= 0 && (pool == 0 || (pooled_k && pooled_v)), "swa_sink_attn_decode_tc: blocks of %d need pooled pools", pool);
+  const int ppb = pool > 0 ? (block_size + pool - 1) / pool : 0;
   B200_REQUIRE(q && k_pool && v_pool && block_table && tok_row && tok_pos && out, "swa_sink_attn_decode_tc: null pointer");
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && window >= 1 && chunk >= 0, "swa_sink_attn_decode_tc: %d query heads over %d kv heads", H, G);
   B200_REQUIRE(v_div >= 1 && G % v_div == 0 && !(sigmoid_bias && sink), "swa_sink_attn_decode_tc: %d key heads sharing values by %d", G, v_div);
@@ -581,7 +637,7 @@ int b200_swa_sink_attn_decode_tc(const float* q, int ldq, const void* k_pool, co
     B200_CUDA_OK(launch_kernel(swa_sink_decode_tc_kernel<M>, grid, dim3(DT_WARPS * 32), smem, st, q, ldq, (const BT*)k_pool,    \
                                (const BT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, window, out, H, G, D,  \
                                Dv, block_size, v_pitch, chunk, softcap, sigmoid_bias, v_div, out_f32, split_p,                  \
-                               split_workspace));                                                                               \
+                               split_workspace, (const BT*)pooled_k, (const BT*)pooled_v, pool, ppb));                          \
   } while (0)
   if (Dv <= 64) DT_LAUNCH(4);
   else if (Dv <= 128) DT_LAUNCH(8);

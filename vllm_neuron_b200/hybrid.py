@@ -46,6 +46,19 @@ Feed-forward: W_down P(W_up h) with the polynomial activation P(z) = a N(z) + b 
 row's RMS.  q / k / v (/ gate) and W_up are ONE GEMM, since both branches read the same h.  State per sequence: the K / V pages
 and the last taps - 1 projected (biased) inputs of the convolutions.
 
+A fourth block style, parallel branches behind TWO RMS norms of the same stream (the "Gerupel" design):
+  x += m (mixer(N1(x)) + ff(N2(x)))   behind a normed token embedding, with logits from the embedding table.  A run of
+layers [loop.start, loop.stop) is repeated loop.times times with the same weights, every repetition with pools and state of
+its own; before a repetition the embedding output (all but the first) and a learned vector per repetition join the stream.
+The mixer 'parallel' is two mixers side by side over the same input, left_scale * left + right_scale * right:
+  * left  -- rotating attention (`RotAttnSpec`) with frequencies rescaled by wavelength bands, a per-head temperature on the
+             scores, a sliding window beside which every block of mask.pool positions that lies wholly before the window is
+             seen as ONE key / value (the mean of the block's cached rows), and a softmax with 1 added to its denominator;
+  * right -- a gated linear recurrence per head (`GatedScanSpec`): S <- diag(f) S + (1 - f) v^T, o = S^T q with q = silu(.),
+             f = lower + (1 - lower) sigmoid(. + bias), a per-head RMS norm of o.  State per sequence: S (fp32).
+Feed-forward: SiLU experts chosen by the largest softmax scores over all experts, weighed on their outputs by the chosen
+scores divided by their sum, times router.scale.
+
 The step is ONE ragged batch (`StepMeta`): portions of prompts and single decoded tokens run through the same kernels, each
 sequence continuing from its KV pages (block table row) and its state slot.  fp32 everywhere the design asks for it
 (residual stream, norms, softmax, router, recurrence); GEMM operands, weights and KV pools are bf16, or fp32 when the model is
@@ -65,7 +78,7 @@ from . import ops
 
 ARCHITECTURE = "Pumopel"
 # block style per architecture: how the norms sit around the sublayers (and which norm it is)
-BLOCK_STYLES = {"Pumopel": "dyt_sandwich", "Kenetar": "rms_post", "Zudarax": "rms_parallel"}
+BLOCK_STYLES = {"Pumopel": "dyt_sandwich", "Kenetar": "rms_post", "Zudarax": "rms_parallel", "Gerupel": "rms_dual"}
 ROT_ATTN_KINDS = ("attention", "attention_2", "attention_3")  # the parallel style's mixers
 _NO_WINDOW = 1 << 30
 
@@ -123,8 +136,8 @@ class DeltaSpec:
 
 @dataclass
 class RotSpec:
-    """Rotary angles over the first `dims` columns, pairs (2i, 2i + 1) or, with `half`, (i, i + dims / 2); `scaling` (YaRN):
-    factor, original, fast, slow."""
+    """Rotary angles over the first `dims` columns, pairs (2i, 2i + 1) or, with `half`, (i, i + dims / 2); `scaling` is either
+    YaRN (factor, original, fast, slow) or wavelength bands (factor, low, high, original)."""
     dims: int
     base: float
     scaling: dict | None = None
@@ -132,13 +145,20 @@ class RotSpec:
 
     def tables(self, positions: int):
         """(cos, sin) fp32 [positions, dims / 2], computed in float64.  Pair i turns by p * f_i, f_i = base^(-2i/dims); with
-        scaling, f_i is blended with f_i / factor by a linear ramp between the pair indices where `fast` and `slow` full turns
-        fit into `original` positions, and cos / sin carry the factor 0.1 ln(factor) + 1."""
+        YaRN scaling, f_i is blended with f_i / factor by a linear ramp between the pair indices where `fast` and `slow` full turns
+        fit into `original` positions, and cos / sin carry the factor 0.1 ln(factor) + 1.  With band scaling (keys low / high) a
+        pair whose wavelength 2 pi / f is below original / high keeps f, one above original / low turns at f / factor, and in
+        between f / factor and f are blended linearly in u = (original / wavelength - low) / (high - low)."""
         i = torch.arange(self.dims // 2, dtype=torch.float64)
         f = self.base ** (-2.0 * i / self.dims)
         mscale = 1.0
         sc = self.scaling
-        if sc:
+        if sc and "low" in sc:
+            factor, low, high, orig = (float(sc[k]) for k in ("factor", "low", "high", "original"))
+            wave = 2 * math.pi / f
+            u = (orig / wave - low) / (high - low)
+            f = torch.where(wave < orig / high, f, torch.where(wave > orig / low, f / factor, (1 - u) * f / factor + u * f))
+        elif sc:
             turns_at = lambda turns: self.dims * math.log(sc["original"] / (2 * math.pi * turns)) / (2 * math.log(self.base))
             lo = max(math.floor(turns_at(sc["fast"])), 0)
             hi = min(math.ceil(turns_at(sc["slow"])), self.dims - 1)
@@ -178,6 +198,10 @@ class RotAttnSpec:
     sigmoid: bool = False    # weights sigmoid(score + bias[head]) instead of a softmax
     diff: float | None = None  # differential attention: two maps per head, this is the constant of lambda and of (1 - diff)
     gate: bool = False       # per-head sigmoid output gate from the mixer's input
+    window: int = 0          # > 0: a query at position i sees keys i - window < j <= i
+    pool: int = 0            # > 0 (with a window): blocks of this many positions wholly before the window are one key / value each
+    unit_sink: bool = False  # softmax with 1 added to its denominator
+    temp: bool = False       # a per-head factor on the scores
 
     @property
     def maps(self) -> int:
@@ -201,6 +225,23 @@ class RotAttnSpec:
 
 
 @dataclass
+class GatedScanSpec:
+    """Gated linear recurrence per head: S <- diag(f) S + (1 - f) v^T, o = S^T q; q, f have `dim` channels, v has `vdim`."""
+    heads: int
+    dim: int
+    vdim: int
+
+
+@dataclass
+class DualMixerSpec:
+    """Two mixers side by side over the same input: left_scale * attention + right_scale * recurrence."""
+    left: RotAttnSpec
+    right: GatedScanSpec
+    left_scale: float
+    right_scale: float
+
+
+@dataclass
 class PolySpec:
     """Dense feed-forward with the polynomial unit-RMS activation."""
     ff: int
@@ -216,7 +257,9 @@ class MoeSpec:
     shared_limit: float = 0.0
     # 'sigmoid_in': weights = sigmoid scores applied to the expert's input, clamped-swish experts;
     # 'softmax_out': weights = softmax over the chosen logits (+ router bias) applied to the experts' outputs, SiLU experts
+    # 'softmax_renorm': weights = softmax over ALL experts, the chosen ones divided by their sum, times `scale`; on the outputs
     route: str = "sigmoid_in"
+    scale: float = 1.0
 
 
 @dataclass
@@ -242,10 +285,20 @@ class HybridConfig:
     bigram: dict | None = None   # buckets, mul_prev, mul_cur
     logit_scale: float = 1.0
     norm_groups: int = 1         # parallel style: equal parts of a row that are normed on their own
+    residual_mult: float = 1.0   # dual-norm style: factor on the sum of a layer's branches
+    loop: dict | None = None     # dual-norm style: start, stop, times -- layers [start, stop) run `times` times in a row
 
     @property
     def style(self) -> str:
         return BLOCK_STYLES[self.name]
+
+    def layer_runs(self) -> list:
+        """[(layer index, repetition or None)] in execution order; a repeated layer appears once per repetition."""
+        n = len(self.layers)
+        if not self.loop:
+            return [(i, None) for i in range(n)]
+        a, b, times = self.loop["start"], self.loop["stop"], self.loop["times"]
+        return [(i, None) for i in range(a)] + [(i, t) for t in range(times) for i in range(a, b)] + [(i, None) for i in range(b, n)]
 
     @staticmethod
     def from_dict(d: dict) -> "HybridConfig":
@@ -255,9 +308,16 @@ class HybridConfig:
             raise ValueError(f"unknown hybrid architecture {name!r}")
         post = BLOCK_STYLES[name] == "rms_post"
         par = BLOCK_STYLES[name] == "rms_parallel"
+        dual = BLOCK_STYLES[name] == "rms_dual"
         for L in d["layers"]:
             m = L["mixer"]
-            if par:
+            if dual:
+                if L["type"] != "parallel":
+                    raise ValueError(f"layer type {L['type']!r} is not part of the {name} design")
+                r = m["right"]
+                mixer = DualMixerSpec(_window_pool_attn_spec(m["left"]), GatedScanSpec(int(r["heads"]), int(r["dim"]), int(r["vdim"])),
+                                      float(m.get("left_scale", 1.0)), float(m.get("right_scale", 1.0)))
+            elif par:
                 if L["type"] not in ROT_ATTN_KINDS:
                     raise ValueError(f"layer type {L['type']!r} is not part of the {name} design")
                 mixer = _rot_attn_spec(L["type"], m)
@@ -285,13 +345,20 @@ class HybridConfig:
                     raise ValueError(f"latent attention: {mixer.rot.dims} rotating columns in a rotated part of {mixer.rot_dim}")
             else:
                 raise ValueError(f"unknown layer type {L['type']!r}")
-            if not par and post != (L["type"] in ("delta", "latent_attention")):
+            if not par and not dual and post != (L["type"] in ("delta", "latent_attention")):
                 raise ValueError(f"layer type {L['type']!r} is not part of the {name} design")
             f = L.get("mlp")
             mlp = None
             if f:
                 kind = f.get("kind", "moe")
-                if par:
+                if dual:
+                    if kind != "moe":
+                        raise ValueError(f"unknown feed-forward kind {kind!r}")
+                    mlp = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]), route="softmax_renorm",
+                                  scale=float(f["router"].get("scale", 1.0)))
+                    if not 1 <= mlp.top <= mlp.experts:
+                        raise ValueError(f"router: top {mlp.top} of {mlp.experts} experts")
+                elif par:
                     if kind != "dense":
                         raise ValueError(f"unknown feed-forward kind {kind!r}")
                     mlp = PolySpec(int(f["ff"]))
@@ -311,9 +378,14 @@ class HybridConfig:
         groups = int(d["norm"].get("groups", 1))
         if int(d["width"]) % groups:
             raise ValueError(f"rows of {d['width']} do not split into {groups} equal norm groups")
+        loop = None
+        if dual and d.get("loop"):
+            loop = {k: int(d["loop"][k]) for k in ("start", "stop", "times")}
+            if not (0 <= loop["start"] < loop["stop"] <= len(layers) and loop["times"] >= 1):
+                raise ValueError(f"loop {loop} over {len(layers)} layers")
         return HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), float(emb.get("scale", 1.0)), layers, name,
                             {k: int(big[k]) for k in ("buckets", "mul_prev", "mul_cur")} if big else None,
-                            float(d.get("logit_scale", 1.0)), groups)
+                            float(d.get("logit_scale", 1.0)), groups, float(d.get("residual_mult", 1.0)) if dual else 1.0, loop)
 
     @staticmethod
     def from_pretrained(path: str) -> "HybridConfig":
@@ -331,9 +403,25 @@ class HybridConfig:
             out["embedding"]["bigram"] = dict(self.bigram)
         if self.style == "rms_post":
             out["logit_scale"] = self.logit_scale
+        if self.style == "rms_dual":
+            del out["embedding"]
+            out["residual_mult"] = self.residual_mult
+            if self.loop:
+                out["loop"] = dict(self.loop)
         for L in self.layers:
             m = L.mixer
-            if isinstance(m, RotAttnSpec):
+            if isinstance(m, DualMixerSpec):
+                a, r = m.left, m.right
+                left = {"heads": a.heads, "kv_heads": a.kv_heads, "dim": a.dim, "vdim": a.vdim, "scale": a.scale}
+                if a.rot is not None:
+                    left["rot"] = {"dims": a.rot.dims, "base": a.rot.base}
+                    if a.rot.scaling:
+                        left["rot"]["scaling"] = dict(a.rot.scaling)
+                if a.window:
+                    left["mask"] = {"size": a.window, **({"pool": a.pool} if a.pool else {})}
+                mixer = {"left": left, "right": {"heads": r.heads, "dim": r.dim, "vdim": r.vdim}, "left_scale": m.left_scale,
+                         "right_scale": m.right_scale}
+            elif isinstance(m, RotAttnSpec):
                 mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
                          "rot": {"dims": m.rot.dims, "base": m.rot.base}}
                 if m.rot.scaling:
@@ -363,6 +451,8 @@ class HybridConfig:
             f = None
             if isinstance(L.mlp, (DenseSpec, PolySpec)):
                 f = {"kind": "dense", "ff": L.mlp.ff}
+            elif L.mlp and L.mlp.route == "softmax_renorm":
+                f = {"kind": "moe", "router": {"experts": L.mlp.experts, "top": L.mlp.top, "scale": L.mlp.scale}, "expert": {"ff": L.mlp.ff}}
             elif L.mlp and L.mlp.route == "softmax_out":
                 f = {"kind": "moe", "router": {"experts": L.mlp.experts, "top": L.mlp.top}, "expert": {"ff": L.mlp.ff}}
             elif L.mlp:
@@ -396,6 +486,25 @@ def _rot_attn_spec(kind: str, m: dict) -> RotAttnSpec:
     return spec
 
 
+def _window_pool_attn_spec(m: dict) -> RotAttnSpec:
+    """The attention half of a 'parallel' mixer: rotary positions (optional band scaling), per-head temperature, unit sink, and a
+    sliding window with pooled blocks before it (mask.size / mask.pool; no mask: every earlier key)."""
+    r = m.get("rot")
+    rot = RotSpec(int(r["dims"]), float(r["base"]), dict(r["scaling"]) if r.get("scaling") else None, half=True) if r else None
+    spec = RotAttnSpec(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), float(m["scale"]), rot, unit_sink=True,
+                       temp=True)
+    if spec.heads % spec.kv_heads:
+        raise ValueError(f"parallel layer: {spec.heads} query heads over {spec.kv_heads} kv heads")
+    if rot is not None and (rot.dims % 2 or rot.dims > spec.dim):
+        raise ValueError(f"parallel layer: {rot.dims} rotating columns in heads of {spec.dim}")
+    mask = m.get("mask") or {}
+    spec.window = int(mask.get("size") or 0)
+    spec.pool = int(mask.get("pool") or 0) if spec.window else 0
+    if spec.window < 0 or spec.pool < 0:
+        raise ValueError(f"parallel layer: window {spec.window}, blocks of {spec.pool}")
+    return spec
+
+
 def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
     """Checkpoint tensor name -> shape (a linear layer's matrix has one row per output)."""
     W = cfg.width
@@ -405,9 +514,15 @@ def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
         s["bigram"] = (cfg.bigram["buckets"] + 1, W)
 
     par = cfg.style == "rms_parallel"
+    dual = cfg.style == "rms_dual"
+    if dual:  # the logits come from the embedding table; the embedding has a norm of its own
+        del s["head"]
+        s["embed.norm"] = (W,)
+        if cfg.loop:
+            s["loop.step"] = (cfg.loop["times"], W)
 
     def norm(n):
-        if post or par:
+        if post or par or dual:
             s[n] = (W,)
         else:
             s[n], s[n + ".b"], s[n + ".alpha"] = (W,), (W,), ()
@@ -415,11 +530,19 @@ def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
     norm("final.norm")
     for i, L in enumerate(cfg.layers):
         p = f"l{i}."
-        for n in ("norm1",) if par else (("norm1",) + (("norm2",) if L.mlp else ())) if post else \
+        for n in ("norm1",) if par else (("norm1",) + (("norm2",) if L.mlp else ())) if post or dual else \
                 (("norm1", "norm1b") + (("norm2", "norm2b") if L.mlp else ())):
             norm(p + n)
         m = L.mixer
-        if isinstance(m, RotAttnSpec):
+        if isinstance(m, DualMixerSpec):
+            a, r = m.left, m.right
+            s.update({p + "mix.left.q": (a.q_cols, W), p + "mix.left.k": (a.k_cols, W), p + "mix.left.v": (a.v_cols, W),
+                      p + "mix.left.temp": (a.heads,), p + "mix.left.o": (W, a.heads * a.vdim),
+                      p + "mix.right.q": (r.heads * r.dim, W), p + "mix.right.f": (r.heads * r.dim, W),
+                      p + "mix.right.f.b": (r.heads * r.dim,), p + "mix.right.lower": (r.heads * r.dim,),
+                      p + "mix.right.v": (r.heads * r.vdim, W), p + "mix.right.norm": (r.vdim,),
+                      p + "mix.right.o": (W, r.heads * r.vdim)})
+        elif isinstance(m, RotAttnSpec):
             s.update({p + "mix.q": (m.q_cols, W), p + "mix.k": (m.k_cols, W), p + "mix.v": (m.v_cols, W),
                       p + "mix.o": (W, m.heads * m.vdim)})
             for n, c in (("q", m.q_cols), ("k", m.k_cols), ("v", m.v_cols)):
@@ -485,6 +608,12 @@ def random_weights(cfg: HybridConfig, seed: int = 0, std: float | None = None) -
             t = 0.5 + 0.5 * torch.rand((), generator=g)
         elif leaf == "vmix":
             t = 0.2 + 0.5 * torch.rand((), generator=g)
+        elif leaf == "temp":
+            t = 0.6 + 0.8 * torch.rand(shape, generator=g)
+        elif leaf == "lower":
+            t = 0.9 * torch.rand(shape, generator=g)
+        elif leaf == "step":
+            t = 0.2 * torch.randn(shape, generator=g)
         elif leaf == "b" and len(shape) == 1:
             t = 0.05 * torch.randn(shape, generator=g)
         elif leaf == "act":
@@ -623,13 +752,18 @@ class HybridCausalLM:
 
         post = cfg.style == "rms_post"
         par = cfg.style == "rms_parallel"
+        dual = cfg.style == "rms_dual"
 
         def norm(name):
-            if post or par:  # RMS norm: weight stored around zero (post-norm) or plain, in groups (parallel)
+            if post or par or dual:  # RMS norm: weight stored around zero (post-norm) or plain (in groups: parallel)
                 return vec(name)
             return (vec(name), vec(name + ".b"), float(get(name + ".alpha").float()))
 
-        self.embed, self.head = lin("embed"), lin("head")
+        self.embed = lin("embed")
+        self.head = self.embed if dual else lin("head")  # dual-norm style: the logits come from the embedding table
+        if dual:
+            self.embed_norm = vec("embed.norm")
+            self.loop_step = vec("loop.step") if cfg.loop else None
         self.final_norm = norm("final.norm")
         self.layers = []
         slots = max_num_seqs + 1
@@ -644,9 +778,21 @@ class HybridCausalLM:
         for i, L in enumerate(cfg.layers):
             p, m = f"l{i}.", L.mixer
             lw = {"spec": L, "norm1": norm(p + "norm1")}
-            if not post and not par:
+            if not post and not par and not dual:
                 lw["norm1b"] = norm(p + "norm1b")
-            if isinstance(m, RotAttnSpec):
+            if isinstance(m, DualMixerSpec):
+                a, r = m.left, m.right
+                if a.rot is not None:
+                    key = (a.rot.dims, a.rot.base, json.dumps(a.rot.scaling, sort_keys=True))
+                    if key not in rot_tables:
+                        rot_tables[key] = tuple(t.to(dev) for t in a.rot.tables(self.max_blocks * block_size))
+                    lw["rot"] = rot_tables[key]
+                # ONE GEMM for everything that reads norm1(x): [left q | k | v | right q | f | v]
+                lw.update(w_in=lin(*(p + "mix." + n for n in ("left.q", "left.k", "left.v", "right.q", "right.f", "right.v"))),
+                          w_o=lin(p + "mix.left.o"), w_o2=lin(p + "mix.right.o"), temp=vec(p + "mix.left.temp"),
+                          sink=torch.zeros((a.heads,), dtype=torch.float32, device=dev),  # exp(0) = the 1 in the denominator
+                          f_bias=vec(p + "mix.right.f.b"), lower=vec(p + "mix.right.lower"), onorm=vec(p + "mix.right.norm"))
+            elif isinstance(m, RotAttnSpec):
                 key = (m.rot.dims, m.rot.base, json.dumps(m.rot.scaling, sort_keys=True))
                 if key not in rot_tables:
                     rot_tables[key] = tuple(t.to(dev) for t in m.rot.tables(self.max_blocks * block_size))
@@ -715,7 +861,7 @@ class HybridCausalLM:
             f = L.mlp
             if f and not par:
                 lw["norm2"] = norm(p + "norm2")
-                if not post:
+                if not post and not dual:
                     lw["norm2b"] = norm(p + "norm2b")
             if isinstance(f, PolySpec):  # W_up rides in w_in
                 lw.update(w_down=lin(p + "mlp.down"), act=vec(p + "mlp.act"))
@@ -732,6 +878,21 @@ class HybridCausalLM:
                     lw["sh_gu"] = lin(p + "mlp.shared.gate", p + "mlp.shared.up")
                     lw["sh_down"] = lin(p + "mlp.shared.down")
             self.layers.append(lw)
+        # dual-norm style: one entry per layer RUN (a repeated layer runs loop.times times with the same weights); every run has
+        # K / V pools, pooled-block pools and recurrent state of its own
+        self.runs = []
+        if dual:
+            for i, rep in cfg.layer_runs():
+                a, r = cfg.layers[i].mixer.left, cfg.layers[i].mixer.right
+                run = {"lw": self.layers[i], "layer": i, "rep": rep, "starts_pass": rep is not None and i == cfg.loop["start"],
+                       "k_pool": torch.zeros((num_blocks, a.kv_heads, block_size, a.dim), dtype=et, device=dev),
+                       "v_pool": torch.zeros((num_blocks, a.kv_heads, block_size, a.vdim), dtype=et, device=dev),
+                       "scan_state": torch.zeros((slots, r.heads, r.vdim, r.dim), dtype=torch.float32, device=dev)}
+                if a.pool:
+                    ppb = -(-block_size // a.pool)
+                    run.update(pk_pool=torch.zeros((num_blocks, a.kv_heads, ppb, a.dim), dtype=et, device=dev),
+                               pv_pool=torch.zeros((num_blocks, a.kv_heads, ppb, a.vdim), dtype=et, device=dev))
+                self.runs.append(run)
         self.block_table = torch.zeros((slots, self.max_blocks), dtype=torch.int32, device=dev)
         self.num_tokens = torch.zeros((slots,), dtype=torch.int32, device=dev)
         self.gemm_ws = None
@@ -741,11 +902,15 @@ class HybridCausalLM:
     # ------------------------------------------------------------------ sizes
     def kv_bytes_per_block(self) -> int:
         es = 2 if self.et == torch.bfloat16 else 4
+        if self.cfg.style == "rms_dual":  # per run: K / V rows of a page and its pooled-block rows
+            return sum(sum(t.shape[1] * t.shape[2] * t.shape[3] * es for n, t in run.items() if n.endswith("_pool")) for run in self.runs)
         return sum(L.mixer.kv_heads * self.block_size * (L.mixer.dim * getattr(L.mixer, "maps", 1) + L.mixer.vdim) * es
                    for L in self.cfg.layers if isinstance(L.mixer, (AttnSpec, RotAttnSpec))) + \
             sum(self.block_size * (L.mixer.kv_rank + L.mixer.rot_dim) * es for L in self.cfg.layers if L.kind == "latent_attention")
 
     def state_bytes_per_slot(self) -> int:
+        if self.cfg.style == "rms_dual":
+            return sum(4 * run["scan_state"][0].numel() for run in self.runs)
         return sum(4 * (L.mixer.heads * L.mixer.state * L.mixer.vdim + (L.mixer.conv - 1) * L.mixer.channels)
                    for L in self.cfg.layers if L.kind == "mamba2") + \
             sum(4 * (L.mixer.heads * L.mixer.dim * L.mixer.vdim + (L.mixer.conv - 1) * L.mixer.channels)
@@ -857,6 +1022,72 @@ class HybridCausalLM:
         self.last_logits = self._linear(h.index_select(0, logit_rows).contiguous(), self.head)
         return self.last_logits
 
+    def _dual_mixer(self, run, h, meta):
+        """Both halves of a 'parallel' mixer from norm1(x) -> (attention branch, recurrence branch), fp32 [T, W] each, unscaled."""
+        lw = run["lw"]
+        m = lw["spec"].mixer
+        a, r = m.left, m.right
+        proj = self._linear(h, lw["w_in"])  # fp32 [T, left q | k | v | right q | f | v]
+        k0 = a.q_cols
+        v0 = k0 + a.k_cols
+        rq0 = v0 + a.v_cols
+        rf0 = rq0 + r.heads * r.dim
+        rv0 = rf0 + r.heads * r.dim
+        cos, sin = lw.get("rot", (None, None))
+        q = ops.qk_norm_rope_kv_write(proj, 0, k0, v0, a.heads, run["k_pool"], run["v_pool"], meta, rot_n=a.rot.dims if a.rot else 0,
+                                      rot_half=True, cos=cos, sin=sin, q_head_scale=lw["temp"])
+        pooled = None
+        if a.pool:  # means of the blocks this step completes, from what the cache now holds
+            ops.kv_pool_mean(run["k_pool"], run["v_pool"], run["pk_pool"], run["pv_pool"], self.block_table, meta, a.pool)
+            pooled = (run["pk_pool"], run["pv_pool"], a.pool)
+        att = ops.swa_sink_attn(q, a.heads, run["k_pool"], run["v_pool"], self.block_table, meta, lw["sink"], a.scale,
+                                a.window or _NO_WINDOW, split_p=True, pooled=pooled)
+        o = ops.gated_scan(proj, rq0, rf0, rv0, lw["f_bias"], lw["lower"], run["scan_state"], meta, r.heads, r.dim, r.vdim)
+        g = ops.head_rmsnorm_gate(o, None, 0, lw["onorm"], self.cfg.eps, r.heads, self.et)
+        return self._linear(att, lw["w_o"]), self._linear(g, lw["w_o2"])
+
+    def _forward_dual(self, tokens, meta, logit_rows, capture):
+        """x += m (ls left(N1 x) + rs right(N1 x) + ff(N2 x)): one pass over the residual per layer run adds the three branches
+        (the experts' rows weighed on the way), what joins the stream ahead of the next run (a repetition's embedding output and
+        step vector), and writes both norms of the result for the next run."""
+        et, cfg, runs = self.et, self.cfg, self.runs
+        x = ops.embed_rmsnorm(tokens, self.embed, self.embed_norm, cfg.eps)
+        x0 = x.clone() if cfg.loop and cfg.loop["times"] > 1 else None
+
+        def entering(k):  # what joins the stream right before run k, and the norms that run reads
+            if k == len(runs):
+                return None, None, self.final_norm, None
+            run = runs[k]
+            rows = x0 if run["starts_pass"] and run["rep"] > 0 else None
+            step = self.loop_step[run["rep"]] if run["starts_pass"] else None
+            return rows, step, run["lw"]["norm1"], run["lw"].get("norm2")
+
+        rows, step, w1, w2 = entering(0)
+        h1, h2 = ops.scaled_add_rmsnorm2(x, cfg.eps, add_rows=rows, add_vec=step, w1=w1, w2=w2, out_dtype=et)
+        for k, run in enumerate(runs):
+            lw = run["lw"]
+            m, f = lw["spec"].mixer, lw["spec"].mlp
+            yl, yr = self._dual_mixer(run, h1, meta)
+            pairs = wt = None
+            if f:
+                idx, wt = ops.moe_topk(self._linear(h2, lw["w_router"]), f.top, mode=ops.ROUTE_SOFTMAX_RENORM)
+                align = ops.moe_align(idx, f.experts, ops.moe_wide_tiles(h2, lw["w_gu"], idx.numel()))
+                pairs = ops.moe_experts(h2, wt, align, lw["w_gu"], lw["w_down"], f.top, act=ops.ACT_SILU, scale_input=False)
+            mult = cfg.residual_mult
+            branches = dict(y1=yl, c1=mult * m.left_scale, y2=yr, c2=mult * m.right_scale, y3=pairs, nsum=f.top if f else 1,
+                            y3_weight=wt, c3=mult * (f.scale if f else 1.0))
+            rows, step, w1, w2 = entering(k + 1)
+            if capture is not None:  # the stream as the layer leaves it, before anything of the next run joins
+                ops.scaled_add_rmsnorm2(x, cfg.eps, **branches)
+                capture.append(x.clone())
+                branches = {}
+            h1, h2 = ops.scaled_add_rmsnorm2(x, cfg.eps, **branches, add_rows=rows, add_vec=step, w1=w1, w2=w2, out_dtype=et)
+        if logit_rows is None or logit_rows.numel() == 0:
+            self.last_logits = None
+            return None
+        self.last_logits = self._linear(h1.index_select(0, logit_rows).contiguous(), self.head)
+        return self.last_logits
+
     def _post_ff(self, lw, h):
         """Feed-forward of the post-norm style -> (fp32 branch rows, rows per token, their weights or None)."""
         f = lw["spec"].mlp
@@ -908,6 +1139,8 @@ class HybridCausalLM:
             return self._forward_post(tokens, meta, logit_rows, capture)
         if self.cfg.style == "rms_parallel":
             return self._forward_parallel(tokens, meta, logit_rows, capture)
+        if self.cfg.style == "rms_dual":
+            return self._forward_dual(tokens, meta, logit_rows, capture)
         et, n = self.et, len(self.layers)
         x = ops.embed_scale(tokens, self.embed, self.cfg.embed_scale)
         h = ops.dyt_norm(x, *self.layers[0]["norm1"], et) if n else None

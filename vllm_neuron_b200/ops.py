@@ -10,7 +10,7 @@ import os
 import torch
 
 from . import _cabi
-from ._cabi import ACT_GELU_TANH, ACT_SILU, ACT_SWISH_CLAMPED, BF16, F32, FP8_E4M3, INT8, ROUTE_SIGMOID, ROUTE_SOFTMAX_TOP, check
+from ._cabi import ACT_GELU_TANH, ACT_SILU, ACT_SWISH_CLAMPED, BF16, F32, FP8_E4M3, INT8, ROUTE_SIGMOID, ROUTE_SOFTMAX_RENORM, ROUTE_SOFTMAX_TOP, check
 
 _QDT = {None: BF16, "bf16": BF16, "fp8": FP8_E4M3, "int8": INT8}
 _TORCH_Q = {FP8_E4M3: torch.float8_e4m3fn, INT8: torch.int8}
@@ -738,15 +738,25 @@ _SWA_PREFILL_LEGACY = bool(os.environ.get("B200_SWA_PREFILL_LEGACY"))
 
 def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink, scale: float, window: int,
                   latent_values: int = 0, *, chunk: int = 0, softcap: float = 0.0, sigmoid_bias=None, out_f32: bool = False,
-                  split_p: bool = False):
+                  split_p: bool = False, pooled=None):
     """q = the first num_heads * D columns of the fp32 rows q_src -> [T, num_heads * Dv] in the pools' element type.
     sink None: ordinary softmax.  latent_values = C > 0: v_pool is ignored and the values are the first C columns of the key
     rows (attention over cached latents: one pool holds both).
     chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0).  softcap > 0:
     scaled scores pass through softcap * tanh(s / softcap).  sigmoid_bias fp32 [H]: weights sigmoid(s + bias[h]), not normalised
     over keys.  A value pool with fewer heads than the key pool: consecutive key heads share a value head (two score maps over
-    the same values).  out_f32: fp32 rows.  split_p: the tensor-core kernel carries the weights as two bf16 terms."""
+    the same values).  out_f32: fp32 rows.  split_p: the tensor-core kernel carries the weights as two bf16 terms.
+    pooled = (pooled key pool, pooled value pool, P) with a window: every block of P positions that lies wholly before a query's
+    window is seen as one key / value, the block's row of the pooled pools (kv_pool_mean), in the same softmax."""
     _cuda(q_src, k_pool, v_pool, block_table, sink, sigmoid_bias)
+    pk, pv, pool = pooled if pooled is not None else (None, None, 0)
+    if pool:
+        _cuda(pk, pv)
+        ppb = -(-k_pool.shape[2] // pool)
+        assert not latent_values and window < (1 << 30) and pk.dtype == k_pool.dtype and pv.dtype == k_pool.dtype
+        assert pk.is_contiguous() and pv.is_contiguous() and pk.shape == (k_pool.shape[0], k_pool.shape[1], ppb, k_pool.shape[3])
+        assert pv.shape == (v_pool.shape[0], v_pool.shape[1], ppb, v_pool.shape[3])
+    pool_args = (_ptr(pk), _ptr(pv), int(pool))
     _f32(q_src, sink, sigmoid_bias)
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     _, g, bs, d = k_pool.shape
@@ -762,8 +772,8 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
     variant = (int(chunk), float(softcap), _ptr(sigmoid_bias), v_div, 1 if out_f32 else 0)
     plain = not chunk and not softcap and sigmoid_bias is None and v_div == 1 and not out_f32
     # the per-launch timer tells the variants apart (their floors differ)
-    tag = "" if plain else "[" + "+".join(n for n, on in (("chunk", chunk), ("cap", softcap), ("sigmoid", sigmoid_bias is not None),
-                                                            ("maps", v_div > 1)) if on) + "]"
+    tag = "" if plain and not pool else "[" + "+".join(n for n, on in (("chunk", chunk), ("cap", softcap), ("sigmoid", sigmoid_bias is not None),
+                                                                       ("maps", v_div > 1), ("pool", pool)) if on) + "]"
     # long prompt portions in bf16 serving, head sizes of 64 / 128 with pages of 32 tokens: the tcgen05 kernel (128-row query
     # tiles, accumulators in tensor memory); B200_SWA_PREFILL_LEGACY=1 keeps the mma.sync kernel (A/B aid)
     if (k_pool.dtype == torch.bfloat16 and meta.max_new >= PREFILL_TC_MIN_TOKENS and sink is None and window >= (1 << 30)
@@ -787,7 +797,7 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
                                                           block_table.stride(0), _ptr(meta.seq_start), _ptr(meta.seq_slot),
                                                           _ptr(meta.seq_pos0), meta.num_seqs, meta.max_new, _ptr(sink), float(scale),
                                                           int(window), _ptr(out), num_heads, g, d, dv, v_pitch, bs, *variant,
-                                                          1 if split_p else 0, _stream()),
+                                                          1 if split_p else 0, *pool_args, _stream()),
                   "b200_swa_sink_attn_prefill")
         return out
     if (plain and latent_values and sink is None and window >= (1 << 30) and k_pool.dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0
@@ -800,6 +810,8 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
         return out
     # long contexts at small batch: several CTAs share a (token, kv head)'s keys, so that every SM has its CTAs
     span = min(getattr(meta, "max_end", 0) or 0, int(window), int(chunk) if chunk else 1 << 30)
+    if pool:  # the blocks before the window count as keys too
+        span += max((getattr(meta, "max_end", 0) or 0) - int(window), 0) // pool
     tc = (k_pool.dtype == torch.bfloat16 and not latent_values and d % 16 == 0 and dv % 16 == 0 and d * v_div <= 512 and dv <= 256
           and q_src.stride(0) % 2 == 0)
     gv = g // v_div
@@ -811,20 +823,21 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
             check(_cabi.load().b200_swa_sink_attn_decode_tc(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                                             block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos), _ptr(sink),
                                                             float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, v_pitch, bs,
-                                                            *variant, 1 if split_p else 0, splits, _ptr(ws), _stream()),
+                                                            *variant, 1 if split_p else 0, splits, _ptr(ws), *pool_args, _stream()),
                   "b200_swa_sink_attn_decode_tc")
         return out
     with _k("swa_sink_attn" + tag):
         check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
                                               _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
                                               _ptr(sink), float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, v_pitch, bs,
-                                              *variant, splits, _ptr(ws), _stream()), "b200_swa_sink_attn")
+                                              *variant, splits, _ptr(ws), *pool_args, _stream()), "b200_swa_sink_attn")
     return out
 
 
 def moe_topk(logits, top: int, bias=None, mode: int = ROUTE_SIGMOID):
     """fp32 router logits [T, E] (+ bias fp32 [E]) -> (expert ids int32 [T, top], routing weights fp32 [T, top]): the sigmoid of
-    each chosen logit (ROUTE_SIGMOID) or the softmax over the chosen logits (ROUTE_SOFTMAX_TOP)."""
+    each chosen logit (ROUTE_SIGMOID), the softmax over the chosen logits (ROUTE_SOFTMAX_TOP), or the softmax over all experts with
+    the chosen scores divided by their sum (ROUTE_SOFTMAX_RENORM)."""
     _cuda(logits, bias)
     _f32(bias)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
@@ -979,16 +992,17 @@ def rmsnorm_cols(src, col0: int, n: int, w, eps: float, out_dtype, *, offset: fl
 
 
 def head_rmsnorm_gate(o, gate_src, gate_col0: int, w, eps: float, heads: int, out_dtype):
-    """o fp32 [T, H * P]: per head o / rms(o) * w [P] * silu(gate), gate = columns gate_col0.. of the fp32 rows gate_src."""
+    """o fp32 [T, H * P]: per head o / rms(o) * w [P] * silu(gate), gate = columns gate_col0.. of the fp32 rows gate_src
+    (gate_src None: the norm alone)."""
     _cuda(o, gate_src, w)
     _f32(o, w)
-    assert gate_src.dtype == torch.float32 and gate_src.stride(1) == 1
+    assert gate_src is None or (gate_src.dtype == torch.float32 and gate_src.stride(1) == 1)
     t, hp = o.shape
     p = hp // heads
     assert w.numel() == p
     out = torch.empty((t, hp), dtype=out_dtype, device=o.device)
     with _k("head_rmsnorm_gate"):
-        check(_cabi.load().b200_head_rmsnorm_gate(_ptr(o), _ptr(gate_src), gate_src.stride(0), gate_col0, _ptr(w), float(eps),
+        check(_cabi.load().b200_head_rmsnorm_gate(_ptr(o), _ptr(gate_src), gate_src.stride(0) if gate_src is not None else 0, gate_col0, _ptr(w), float(eps),
                                                   _ptr(out), _edt(out), t, heads, p, _stream()), "b200_head_rmsnorm_gate")
     return out
 
@@ -1105,12 +1119,14 @@ def diff_head_norm_gate(a, lam: float, post: float, gate_src, gate_col0: int, ep
 
 
 def qk_norm_rope_kv_write(src, q_col0: int, k_col0: int, v_col0: int, heads: int, k_pool, v_pool, meta, *, q_norm=None,
-                          k_norm=None, eps: float = 0.0, rot_n: int = 0, rot_half: bool = True, cos=None, sin=None):
+                          k_norm=None, eps: float = 0.0, rot_n: int = 0, rot_half: bool = True, cos=None, sin=None, q_head_scale=None):
     """fp32 rows src = [.. q: heads * D .. k: G * D .. v: Gv * Dv ..] -> q fp32 [T, heads * D] (normed over the whole projection
     when q_norm is given, leading rot_n columns of every head rotated by the token's position), and the step's keys (same
-    treatment) and values written into the pools [num_blocks, G, block_size, D] / [num_blocks, Gv, block_size, Dv]."""
-    _cuda(src, k_pool, v_pool, q_norm, k_norm, cos, sin)
-    _f32(q_norm, k_norm, cos, sin)
+    treatment) and values written into the pools [num_blocks, G, block_size, D] / [num_blocks, Gv, block_size, Dv].
+    q_head_scale fp32 [heads]: q of head h is multiplied by it (a per-head temperature of the scores)."""
+    _cuda(src, k_pool, v_pool, q_norm, k_norm, cos, sin, q_head_scale)
+    _f32(q_norm, k_norm, cos, sin, q_head_scale)
+    assert q_head_scale is None or q_head_scale.numel() == heads
     assert src.dtype == torch.float32 and src.stride(1) == 1 and k_pool.dtype == v_pool.dtype
     assert k_pool.is_contiguous() and v_pool.is_contiguous()
     _, g, bs, d = k_pool.shape
@@ -1122,6 +1138,82 @@ def qk_norm_rope_kv_write(src, q_col0: int, k_col0: int, v_col0: int, heads: int
         check(_cabi.load().b200_qk_norm_rope_kv_write(_ptr(src), src.stride(0), q_col0, k_col0, v_col0, _ptr(q_norm), _ptr(k_norm),
                                                       float(eps), int(rot_n), 1 if rot_half else 0, _ptr(cos), _ptr(sin),
                                                       _ptr(meta.tok_pos), _ptr(meta.slot_mapping), _ptr(q), _ptr(k_pool),
-                                                      _ptr(v_pool), _edt(k_pool), t, heads, g, gv, d, dv, bs, _stream()),
+                                                      _ptr(v_pool), _edt(k_pool), t, heads, g, gv, d, dv, bs, _ptr(q_head_scale),
+                                                      _stream()),
               "b200_qk_norm_rope_kv_write")
     return q
+
+
+# ------------------------------------------------------------------ dual-norm parallel decoders (window + pooled-block attention
+# beside a gated linear recurrence)
+def embed_rmsnorm(tokens, table, w, eps: float):
+    """tokens int32 [T] -> fp32 [T, W] = RMS norm of table[token], times w."""
+    _cuda(tokens, table, w)
+    _f32(w)
+    assert tokens.dtype == torch.int32 and table.is_contiguous()
+    t, (v, width) = tokens.numel(), table.shape
+    out = torch.empty((t, width), dtype=torch.float32, device=table.device)
+    with _k("embed_rmsnorm"):
+        check(_cabi.load().b200_embed_rmsnorm(_ptr(tokens), _ptr(table), _edt(table), _ptr(w), float(eps), _ptr(out), t, width, v,
+                                              _stream()), "b200_embed_rmsnorm")
+    return out
+
+
+def scaled_add_rmsnorm2(x, eps: float, *, y1=None, c1: float = 1.0, y2=None, c2: float = 1.0, y3=None, nsum: int = 1, y3_weight=None,
+                        c3: float = 1.0, add_rows=None, add_vec=None, w1=None, w2=None, out_dtype=None):
+    """x += c1 y1 + c2 y2 + c3 sum_k y3_weight[t, k] y3[t nsum + k] + add_rows + add_vec, in place (fp32; every term optional);
+    returns (RMS norm of x times w1, the same times w2) in out_dtype, None for a weight that is not given."""
+    _cuda(x, y1, y2, y3, y3_weight, add_rows, add_vec, w1, w2)
+    _f32(x, y3, y3_weight, add_rows, add_vec, w1, w2)
+    t, width = x.shape
+    for y in (y1, y2):
+        assert y is None or (y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (t, width))
+    assert y3 is None or (y3.shape == (t * nsum, width) and (y3_weight is None or y3_weight.numel() == t * nsum))
+    assert add_rows is None or add_rows.shape == (t, width)
+    assert add_vec is None or add_vec.numel() == width
+    o1 = torch.empty((t, width), dtype=out_dtype, device=x.device) if w1 is not None else None
+    o2 = torch.empty((t, width), dtype=out_dtype, device=x.device) if w2 is not None else None
+    with _k("scaled_add_rmsnorm2"):
+        check(_cabi.load().b200_scaled_add_rmsnorm2(_ptr(x), _ptr(y1), y1.stride(0) if y1 is not None else 0, float(c1), _ptr(y2),
+                                                    y2.stride(0) if y2 is not None else 0, float(c2), _ptr(y3), int(nsum),
+                                                    _ptr(y3_weight), float(c3), _ptr(add_rows), _ptr(add_vec), _ptr(w1), _ptr(o1),
+                                                    _ptr(w2), _ptr(o2), float(eps), _edt(out_dtype) if out_dtype is not None else F32,
+                                                    t, width, _stream()), "b200_scaled_add_rmsnorm2")
+    return o1, o2
+
+
+def kv_pool_mean(k_pool, v_pool, pk_pool, pv_pool, block_table, meta, pool: int):
+    """For every token of the step that closes a block of `pool` positions: the mean of the block's cached key rows and value rows
+    -> the pooled pools [num_blocks, G, ceil(block_size / pool), D | Dv] (entry of a block: page of its last position)."""
+    _cuda(k_pool, v_pool, pk_pool, pv_pool, block_table)
+    _, g, bs, d = k_pool.shape
+    _, gv, _, dv = v_pool.shape
+    ppb = -(-bs // pool)
+    assert pk_pool.shape == (k_pool.shape[0], g, ppb, d) and pv_pool.shape == (v_pool.shape[0], gv, ppb, dv)
+    assert pk_pool.dtype == k_pool.dtype == v_pool.dtype == pv_pool.dtype and pk_pool.is_contiguous() and pv_pool.is_contiguous()
+    assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    with _k("kv_pool_mean"):
+        check(_cabi.load().b200_kv_pool_mean(_ptr(k_pool), _ptr(v_pool), _ptr(pk_pool), _ptr(pv_pool), _edt(k_pool), _ptr(block_table),
+                                             block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos), _ptr(meta.slot_mapping),
+                                             meta.num_tokens, g, gv, d, dv, bs, int(pool), _stream()), "b200_kv_pool_mean")
+
+
+def gated_scan(proj, q_col0: int, f_col0: int, v_col0: int, f_bias, lower, state, meta, heads: int, dim: int, vdim: int):
+    """Gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T q per head over a ragged batch.  Raw q / f / v are the columns
+    q_col0 / f_col0 / v_col0 of the fp32 rows proj; q = silu(raw), f = lower + (1 - lower) sigmoid(raw + f_bias) are written back
+    IN PLACE.  state fp32 [slots, H, vdim, dim] (transposed) updated in place; returns o fp32 [T, H * vdim]."""
+    _cuda(proj, f_bias, lower, state)
+    _f32(f_bias, lower, state)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.shape[1:] == (heads, vdim, dim)
+    assert f_bias.numel() == heads * dim == lower.numel()
+    t = proj.shape[0]
+    out = torch.empty((t, heads * vdim), dtype=torch.float32, device=proj.device)
+    lib = _cabi.load()
+    with _k("gated_scan_prep"):
+        check(lib.b200_gated_scan_prep(_ptr(proj), proj.stride(0), q_col0, f_col0, heads * dim, _ptr(f_bias), _ptr(lower), t,
+                                       _stream()), "b200_gated_scan_prep")
+    with _k("gated_scan"):
+        check(lib.b200_gated_scan(_ptr(proj), proj.stride(0), q_col0, f_col0, v_col0, _ptr(state), _ptr(meta.seq_start),
+                                  _ptr(meta.seq_slot), _ptr(meta.seq_pos0), _ptr(out), meta.num_seqs, heads, dim, vdim, _stream()),
+              "b200_gated_scan")
+    return out

@@ -7,7 +7,9 @@ Two families are served:
   * hybrid decoders (`HybridCausalLM`): config.json lists the layers; a step is one ragged batch.  "Pumopel": state-space /
     windowed-attention mixers, Dynamic-Tanh norms, MoE; "Kenetar": delta-rule / latent-attention mixers, post-norm RMS,
     bigram embedding, dense or MoE feed-forward; "Zudarax": parallel mixer / feed-forward branches behind one grouped RMS
-    norm, three rotating-attention variants (chunked + soft-capped, differential, sigmoid), polynomial activation.
+    norm, three rotating-attention variants (chunked + soft-capped, differential, sigmoid), polynomial activation;
+    "Gerupel": parallel branches behind two RMS norms, a mixer that is windowed attention with pooled far blocks beside a gated
+    linear recurrence, repeated layer runs with shared weights, MoE, logits from the embedding table.
 The reference resolves the architecture the same way -- `hf_config.architectures[0]` picks the NxDI model class
 (vllm_neuron/worker/neuronx_distributed_model_loader.py:612-660).
 """
@@ -76,6 +78,7 @@ MODEL_REGISTRY: dict[str, ModelEntry] = {
     "Pumopel": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
     "Kenetar": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
     "Zudarax": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
+    "Gerupel": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
 }
 
 
