@@ -55,11 +55,11 @@ def rotate_half(x, rot):
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
 
 
-def window_pool_attention(q, k, v, scale, temp, size, pool):
+def window_pool_attention(q, k, v, scale, temp, size, pool, pool_dtype=None):
     """q [T, H, D], k [T, G, D], v [T, G, Dv] (k already rotated).  Query i sees keys i - size < j <= i and, for every block
     b of `pool` positions with b pool + pool - 1 <= i - size, the mean key and mean value of the block.  Weights
     exp(s) / (1 + sum exp(s)) over tokens and blocks together; scores q . k * scale * temp[head].  size None: every earlier
-    key, no blocks."""
+    key, no blocks.  pool_dtype: the block means pass through this type (a cache of that type holds them)."""
     T, H, D = q.shape
     G, Dv = k.shape[1], v.shape[2]
     rep = H // G
@@ -68,6 +68,8 @@ def window_pool_attention(q, k, v, scale, temp, size, pool):
     if nblk:
         kb = k[: nblk * pool].view(nblk, pool, G, D).mean(1)
         vb = v[: nblk * pool].view(nblk, pool, G, Dv).mean(1)
+        if pool_dtype is not None:
+            kb, vb = kb.to(pool_dtype).to(q.dtype), vb.to(pool_dtype).to(q.dtype)
     for i in range(T):
         lo = 0 if size is None else max(0, i - size + 1)
         nb = 0 if not nblk else max(0, (i - size + 1) // pool)
@@ -96,7 +98,7 @@ def left_mixer(h, W, p, m, cache_dtype=None):
     if cache_dtype is not None:
         k, v = k.to(cache_dtype).to(h.dtype), v.to(cache_dtype).to(h.dtype)
     mask = m.get("mask") or {}
-    o = window_pool_attention(q, k, v, float(m["scale"]), W[p + "temp"], mask.get("size"), int(mask.get("pool") or 0))
+    o = window_pool_attention(q, k, v, float(m["scale"]), W[p + "temp"], mask.get("size"), int(mask.get("pool") or 0), cache_dtype)
     return o.reshape(T, H * Dv) @ W[p + "o"].T
 
 
