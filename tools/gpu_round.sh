@@ -36,7 +36,7 @@ if [[ "$ARGS" == *" launches "* ]]; then
 fi
 if [[ "$ARGS" == *" ncufull "* ]]; then
   timeout 600 $SHORT > gpurun_out/plain2.log 2>&1 &&
-  timeout 900 ncu --set full --clock-control none --import-source on -k regex:${NCU_KERNEL:-paged_attn_decode_kernel} -s ${NCU_SKIP:-40} -c 3 \
+  timeout 900 ncu --set full --clock-control none -k regex:${NCU_KERNEL:-paged_attn_decode_kernel} -s ${NCU_SKIP:-40} -c 3 \
       -f -o gpurun_out/prof_${NCU_TAG:-attn} $SHORT > gpurun_out/ncu_full.log 2>&1
   echo "ncufull exit=$?" | tee -a gpurun_out/summary.txt
   tail -3 gpurun_out/ncu_full.log

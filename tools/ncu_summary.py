@@ -4,7 +4,7 @@
   python tools/ncu_summary.py full gpurun_out/prof_attn.ncu-rep OUT.json  -> selected metrics per launch (needs `ncu -i`)
 
 The launch list comes from `ncu --metrics gpu__time_duration.sum --clock-control none` (cold caches, serialised: shares
-only); the full capture from `ncu --set full --clock-control none --import-source on` (tools/gpu_round.sh).
+only); the full capture from `ncu --set full --clock-control none` (tools/gpu_round.sh).
 """
 from __future__ import annotations
 
