@@ -716,11 +716,14 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (result is then NOT the headline)")
     ap.add_argument("--attn-traffic", type=float, default=None,
                     help="dram bytes read+written per attention launch from the committed ncu --set full capture")
-    ap.add_argument("--hybrid", default="", choices=["", "small", "1b", "all", "kenetar-small", "kenetar-1b", "zudarax-small", "zudarax-1b"],
+    ap.add_argument("--hybrid", default="", choices=["", "small", "1b", "all", "kenetar-small", "kenetar-1b", "zudarax-small", "zudarax-1b",
+                                                       "gerupel-small", "gerupel-1b"],
                     help="instead of the headline workload: prefill / decode throughput and per-kernel floors of the hybrid "
                          "(state-space + windowed attention + MoE) decoder beside the dense decoder at equal size, or (kenetar-*) of "
                          "the delta-rule + latent-attention decoder beside that hybrid at equal size, or (zudarax-*) of the parallel-branch "
-                         "decoder with chunked / differential / sigmoid attention beside the dense decoder; one JSON line per size "
+                         "decoder with chunked / differential / sigmoid attention beside the dense decoder, or (gerupel-*) of the "
+                         "dual-norm parallel decoder (window + pooled-block attention beside a gated recurrence) beside that hybrid; "
+                         "one JSON line per size "
                          "(vllm_neuron_b200/hybrid_bench.py)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -493,7 +493,7 @@ int b200_gated_scan_prep(float* proj, int ld, int q_col0, int f_col0, int n, con
                          void* stream);
 /* Gated linear recurrence over a ragged batch: per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q, f [H][D]
  * and v [H][P] the columns q_col0 / f_col0 / v_col0 of the fp32 rows proj.  state fp32 [slots][H][P][D] (transposed), read for
- * sequences with seq_pos0 > 0 and written back for all; out fp32 [T][H * P].  D <= 256, else B200_ERR_UNSUPPORTED. */
+ * sequences with seq_pos0 > 0 and written back for all; out fp32 [T][H * P].  D <= 512, else B200_ERR_UNSUPPORTED. */
 int b200_gated_scan(const float* proj, int ld, int q_col0, int f_col0, int v_col0, float* state, const int32_t* seq_start,
                     const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int D, int P, void* stream);
 /* gate_up fp32 [T][2 ff] (gate first): out = act(gate) * up, act = B200_ACT_SILU or B200_ACT_GELU_TANH */

@@ -308,7 +308,7 @@ def test_unequal_sequences_in_one_step_see_their_own_blocks(kv_dtype):
 
 
 # ------------------------------------------------------------------------------------------------ gated linear recurrence
-@pytest.mark.parametrize("H,D,P,lead", [(2, 10, 7, 3), (3, 48, 64, 0), (1, 33, 20, 1), (2, 128, 32, 4), (1, 256, 16, 8), (4, 4, 5, 0)])
+@pytest.mark.parametrize("H,D,P,lead", [(2, 10, 7, 3), (3, 48, 64, 0), (1, 33, 20, 1), (2, 128, 32, 4), (1, 256, 16, 8), (4, 4, 5, 0), (1, 500, 3, 0)])
 def test_gated_recurrence_over_portions_slots_and_reuse(H, D, P, lead):
     """Raw projections -> silu / bounded forget gate -> recurrence, for a sequence cut into portions beside another sequence in the
     same steps; then the first sequence's slot is taken over by a new one, which must not see the old state."""

@@ -4,10 +4,12 @@
 // where q = silu(raw q), f = lower + (1 - lower) sigmoid(raw f + bias) per channel, and v has P columns per head: the "key" of
 // the outer product is 1 - f, there is no other key and no scale.
 //   * gated_scan_prep: turns the raw q and f columns of the projection rows into q and f IN PLACE (fp32);
-//   * gated_scan: CTA = (16 value columns, head, sequence), 128 threads = 8 slices of the D state rows x 16 columns; a thread
-//     keeps its 4 KR state elements in registers (rows 32 k + 4 slice + e: a warp reads a token's f and q as conflict-free
-//     float4), tokens are staged 16 at a time with cp.async one chunk ahead, the update is S = v + f (S - v) (one subtraction
-//     and one FMA; no 1 - f that would lose digits where f is close to 1), the row reduction of o three shuffles.
+//   * gated_scan: CTA = (16 value columns, head, sequence), 256 threads = 16 slices of the D state rows x 16 columns; a thread
+//     keeps its 4 KR state elements in registers (rows 64 k + 4 slice + e: a half-warp reads a token's f and q as conflict-free
+//     float4), tokens are staged 16 at a time with cp.async one chunk ahead and taken four at a time (the four row reductions
+//     of o, four shuffles each, run under the next tokens' updates), the update is S = v + f (S - v) (one subtraction and one
+//     FMA; no 1 - f that would lose digits where f is close to 1).  Launched without programmatic early start: its few
+//     long-running CTAs must spread evenly over the SMs.
 // The state is stored TRANSPOSED, [slots][H][P][D], so that a warp's loads and stores of it are whole 128-byte lines.
 // A sequence whose portion starts at position 0 ignores what its slot held.
 #include "hybrid_common.cuh"
@@ -15,7 +17,7 @@
 namespace b200 {
 
 constexpr int GS_COLS = 16;     // value columns per CTA
-constexpr int GS_SLICES = 8;    // lanes that share a column (slices of the state rows)
+constexpr int GS_SLICES = 16;   // lanes that share a column (slices of the state rows)
 constexpr int GS_THREADS = GS_COLS * GS_SLICES;
 constexpr int GS_CHUNK = 16;    // tokens staged per round
 
@@ -45,7 +47,7 @@ __global__ void __launch_bounds__(GS_THREADS)
                       const int32_t* __restrict__ seq_pos0, float* __restrict__ out, int H, int D, int P, int vec) {
   griddep_launch();
   griddep_wait();
-  constexpr int Dp = 32 * KR;
+  constexpr int Dp = 4 * GS_SLICES * KR;
   extern __shared__ __align__(16) float gs_sm[];
   float* qs = gs_sm;                              // [2][GS_CHUNK][Dp]
   float* fs = qs + 2 * GS_CHUNK * Dp;             // [2][GS_CHUNK][Dp]
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(GS_THREADS)
   if (seq_pos0[sq] > 0 && col_ok) {
 #pragma unroll
     for (int k = 0; k < KR; ++k) {
-      const int i = 32 * k + 4 * r;
+      const int i = 4 * GS_SLICES * k + 4 * r;
       if (vec && i + 3 < D) {
         const float4 a = *reinterpret_cast<const float4*>(st + i);
         S[k][0] = a.x, S[k][1] = a.y, S[k][2] = a.z, S[k][3] = a.w;
@@ -118,27 +120,47 @@ __global__ void __launch_bounds__(GS_THREADS)
     }
     __syncthreads();
     const int cn = n - ch * GS_CHUNK < GS_CHUNK ? n - ch * GS_CHUNK : GS_CHUNK;
-    for (int tk = 0; tk < cn; ++tk) {
+    // one token: the thread's state elements, and its share of o = S^T q (two accumulators: half the dependent chain)
+    auto token = [&](int tk) -> float {
       const float v = vs[(buf * GS_CHUNK + tk) * GS_COLS + c];
       const float* fr = fs + (buf * GS_CHUNK + tk) * Dp + 4 * r;
       const float* qr = qs + (buf * GS_CHUNK + tk) * Dp + 4 * r;
-      float o = 0.f;
+      float oa = 0.f, ob = 0.f;
 #pragma unroll
       for (int k = 0; k < KR; ++k) {
-        const float4 f4 = *reinterpret_cast<const float4*>(fr + 32 * k);
-        const float4 q4 = *reinterpret_cast<const float4*>(qr + 32 * k);
+        const float4 f4 = *reinterpret_cast<const float4*>(fr + 4 * GS_SLICES * k);
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + 4 * GS_SLICES * k);
         S[k][0] = fmaf(f4.x, S[k][0] - v, v);
         S[k][1] = fmaf(f4.y, S[k][1] - v, v);
         S[k][2] = fmaf(f4.z, S[k][2] - v, v);
         S[k][3] = fmaf(f4.w, S[k][3] - v, v);
-        o = fmaf(S[k][0], q4.x, o);
-        o = fmaf(S[k][1], q4.y, o);
-        o = fmaf(S[k][2], q4.z, o);
-        o = fmaf(S[k][3], q4.w, o);
+        oa = fmaf(S[k][0], q4.x, oa);
+        ob = fmaf(S[k][1], q4.y, ob);
+        oa = fmaf(S[k][2], q4.z, oa);
+        ob = fmaf(S[k][3], q4.w, ob);
       }
+      return oa + ob;
+    };
+    auto reduce = [&](float o) -> float {  // over the 16 lanes that share the column
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       o += __shfl_xor_sync(0xffffffffu, o, 4);
+      o += __shfl_xor_sync(0xffffffffu, o, 8);
+      return o;
+    };
+    int tk = 0;
+    for (; tk + 4 <= cn; tk += 4) {
+      float o0 = token(tk), o1 = token(tk + 1), o2 = token(tk + 2), o3 = token(tk + 3);
+      o0 = reduce(o0), o1 = reduce(o1), o2 = reduce(o2), o3 = reduce(o3);
+      if (r == 0) {
+        os[tk * GS_COLS + c] = o0;
+        os[(tk + 1) * GS_COLS + c] = o1;
+        os[(tk + 2) * GS_COLS + c] = o2;
+        os[(tk + 3) * GS_COLS + c] = o3;
+      }
+    }
+    for (; tk < cn; ++tk) {
+      const float o = reduce(token(tk));
       if (r == 0) os[tk * GS_COLS + c] = o;
     }
     __syncthreads();  // the chunk's outputs are complete, and its buffer may be refilled
@@ -151,7 +173,7 @@ __global__ void __launch_bounds__(GS_THREADS)
     // state rows past D were fed f = 0 and hold v: they are not part of the state
 #pragma unroll
     for (int k = 0; k < KR; ++k) {
-      const int i = 32 * k + 4 * r;
+      const int i = 4 * GS_SLICES * k + 4 * r;
       if (vec && i + 3 < D) {
         *reinterpret_cast<float4*>(st + i) = make_float4(S[k][0], S[k][1], S[k][2], S[k][3]);
       } else {
@@ -185,8 +207,8 @@ int b200_gated_scan(const float* proj, int ld, int q_col0, int f_col0, int v_col
                     const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int D, int P, void* stream) {
   B200_REQUIRE(proj && state && seq_start && seq_slot && seq_pos0 && out, "gated_scan: null pointer");
   B200_REQUIRE(H >= 1 && D >= 1 && P >= 1, "gated_scan: bad shape");
-  if (D > 256) {
-    set_last_error("gated_scan: %d state rows per head exceed 256", D);
+  if (D > 512) {
+    set_last_error("gated_scan: %d state rows per head exceed 512", D);
     return B200_ERR_UNSUPPORTED;
   }
   if (B <= 0) return B200_OK;
@@ -197,15 +219,15 @@ int b200_gated_scan(const float* proj, int ld, int q_col0, int f_col0, int v_col
   cudaStream_t st = (cudaStream_t)stream;
 #define GS_LAUNCH(KR)                                                                                                     \
   do {                                                                                                                    \
-    const size_t smem = (size_t)(4 * GS_CHUNK * 32 * KR + 3 * GS_CHUNK * GS_COLS) * 4;                                    \
+    const size_t smem = (size_t)(4 * GS_CHUNK * 4 * GS_SLICES * KR + 3 * GS_CHUNK * GS_COLS) * 4;                         \
     if (smem > 48 * 1024)                                                                                                 \
       B200_CUDA_OK(cudaFuncSetAttribute(gated_scan_kernel<KR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    B200_CUDA_OK(launch_kernel(gated_scan_kernel<KR>, grid, dim3(GS_THREADS), smem, st, proj, ld, q_col0, f_col0, v_col0, \
-                               state, seq_start, seq_slot, seq_pos0, out, H, D, P, vec));                                \
+    B200_CUDA_OK(launch_kernel_serial(gated_scan_kernel<KR>, grid, dim3(GS_THREADS), smem, st, proj, ld, q_col0, f_col0,  \
+                                      v_col0, state, seq_start, seq_slot, seq_pos0, out, H, D, P, vec));                 \
   } while (0)
-  if (D <= 32) GS_LAUNCH(1);
-  else if (D <= 64) GS_LAUNCH(2);
-  else if (D <= 128) GS_LAUNCH(4);
+  if (D <= 64) GS_LAUNCH(1);
+  else if (D <= 128) GS_LAUNCH(2);
+  else if (D <= 256) GS_LAUNCH(4);
   else GS_LAUNCH(8);
 #undef GS_LAUNCH
   return B200_OK;

@@ -247,13 +247,18 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const float* __restrict__ src, 
 // the cache holds), sums them in fp32, divides by `pool` and writes the mean into the pooled pools
 // PK [num_blocks][G][ppb][D], PV [num_blocks][Gv][ppb][Dv], ppb = ceil(block_size / pool): the entry of block b lives in the page
 // that holds the block's last position e, at index (e % block_size) / pool.  Runs after the step's keys and values are written.
+constexpr int PM_THREADS = 256;
+constexpr int PM_ROWS = 64;  // positions whose rows are looked up per round
+
 template <typename KT>
-__global__ void kv_pool_mean_kernel(const KT* __restrict__ k_pool, const KT* __restrict__ v_pool, KT* __restrict__ pk_pool,
-                                    KT* __restrict__ pv_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
-                                    const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos,
-                                    const int64_t* __restrict__ slots, int G, int Gv, int D, int Dv, int bs, int pool, int ppb) {
+__global__ void __launch_bounds__(PM_THREADS)
+    kv_pool_mean_kernel(const KT* __restrict__ k_pool, const KT* __restrict__ v_pool, KT* __restrict__ pk_pool,
+                        KT* __restrict__ pv_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
+                        const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos,
+                        const int64_t* __restrict__ slots, int G, int Gv, int D, int Dv, int bs, int pool, int ppb) {
   griddep_launch();
   griddep_wait();
+  __shared__ int32_t pg[PM_ROWS], po[PM_ROWS];  // page and offset in the page of the round's positions
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   if (slots[t] < 0 || (pos + 1) % pool != 0) return;
@@ -262,14 +267,54 @@ __global__ void kv_pool_mean_kernel(const KT* __restrict__ k_pool, const KT* __r
   const int64_t dst_blk = bt[pos / bs];
   const int dst_idx = (pos % bs) / pool;
   const float inv = 1.0f / (float)pool;
-  for (int i = threadIdx.x; i < G * D + Gv * Dv; i += blockDim.x) {
-    const bool key = i < G * D;
-    const int c = key ? i : i - G * D, W = key ? D : Dv, N = key ? G : Gv;
-    const int g = c / W, d = c - g * W;
-    const KT* src = key ? k_pool : v_pool;
-    float s = 0.f;
-    for (int p = first; p <= pos; ++p) s += ldf(src, (((int64_t)bt[p / bs] * N + g) * bs + p % bs) * W + d);
-    stf(key ? pk_pool : pv_pool, ((dst_blk * N + g) * ppb + dst_idx) * W + d, s * inv);
+  const int cols = G * D + Gv * Dv;
+  // a thread owns columns tid, tid + PM_THREADS, ... (up to 8 of them in registers; wider rows take further passes)
+  for (int c0 = 0; c0 < cols; c0 += 8 * PM_THREADS) {
+    float acc[8];
+    int64_t off[8];  // element offset of the column inside a page, without the row: (g * rows_per_page) * W + d
+    int width[8];
+    const KT* src[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = c0 + u * PM_THREADS + threadIdx.x;
+      const bool key = i < G * D;
+      const int c = key ? i : i - G * D, W = key ? D : Dv;
+      const int g = c / W, d = c - g * W;
+      acc[u] = 0.f;
+      width[u] = i < cols ? W : 0;
+      src[u] = key ? k_pool : v_pool;
+      off[u] = ((int64_t)g * bs) * W + d;
+    }
+    for (int p0 = first; p0 <= pos; p0 += PM_ROWS) {
+      const int np = pos + 1 - p0 < PM_ROWS ? pos + 1 - p0 : PM_ROWS;
+      __syncthreads();
+      if (threadIdx.x < np) {
+        const int p = p0 + threadIdx.x;
+        pg[threadIdx.x] = bt[p / bs];
+        po[threadIdx.x] = p % bs;
+      }
+      __syncthreads();
+#pragma unroll 4
+      for (int k = 0; k < np; ++k) {
+        const int64_t blk = pg[k];
+        const int o = po[k];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (width[u]) {
+            const int N = src[u] == k_pool ? G : Gv;
+            acc[u] += ldf(src[u], (blk * N * bs + o) * width[u] + off[u]);
+          }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = c0 + u * PM_THREADS + threadIdx.x;
+      if (i >= cols) continue;
+      const bool key = i < G * D;
+      const int c = key ? i : i - G * D, W = key ? D : Dv, N = key ? G : Gv;
+      const int g = c / W, d = c - g * W;
+      stf(key ? pk_pool : pv_pool, ((dst_blk * N + g) * ppb + dst_idx) * W + d, acc[u] * inv);
+    }
   }
 }
 
@@ -594,7 +639,7 @@ int b200_kv_pool_mean(const void* k_pool, const void* v_pool, void* pooled_k, vo
   if (T <= 0) return B200_OK;
   const int ppb = (block_size + pool - 1) / pool;
   B200_DISPATCH_ELEM(kv_dtype, KT,
-                     B200_CUDA_OK(launch_kernel(kv_pool_mean_kernel<KT>, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const KT*)k_pool,
+                     B200_CUDA_OK(launch_kernel(kv_pool_mean_kernel<KT>, dim3(T), dim3(PM_THREADS), 0, (cudaStream_t)stream, (const KT*)k_pool,
                                                 (const KT*)v_pool, (KT*)pooled_k, (KT*)pooled_v, block_table, bt_stride, tok_row,
                                                 tok_pos, slot_mapping, G, Gv, D, Dv, block_size, pool, ppb)));
   return B200_OK;

@@ -1,6 +1,7 @@
 """Prefill / decode throughput of the hybrid decoders (bench.py --hybrid): the Pumopel design next to the dense Llama decoder
-at equal size (`small`, `1b`), the Kenetar design next to Pumopel at equal size (`kenetar-small`, `kenetar-1b`), and the
-Zudarax design next to the dense Llama decoder at equal size (`zudarax-small`, `zudarax-1b`).
+at equal size (`small`, `1b`), the Kenetar design next to Pumopel at equal size (`kenetar-small`, `kenetar-1b`), the
+Zudarax design next to the dense Llama decoder at equal size (`zudarax-small`, `zudarax-1b`), and the Gerupel design next to
+Pumopel (its closest relative: windowed sink attention, a recurrence, experts) at equal size (`gerupel-small`, `gerupel-1b`).
 
 For each size: random weights, both models in bf16 on one GPU, same width / layer count / vocabulary; the dense model's
 intermediate size equals the hybrid's ACTIVE feed-forward width (top * ff + shared ff) so a token costs about the same FLOPs.
@@ -49,6 +50,65 @@ ZUDARAX_MIXERS = {
     "1b": dict(heads=16, kv_heads=4, dim=128, vdim=128, conv=4, chunk=1024, softcap=30.0),
     "small": dict(heads=16, kv_heads=4, dim=64, vdim=64, conv=4, chunk=512, softcap=30.0),
 }
+
+
+# the dual-norm parallel design at the same width / vocabulary / attention sizes and as many layer RUNS: six layers of which the
+# third and fourth run twice; window as the hybrid's, blocks of `pool` positions behind it; the recurrence as wide as the
+# attention; top * ff = the hybrid's active feed-forward width (it has no shared expert)
+GERUPEL_MIXERS = {
+    "1b": dict(pool=16, right=dict(heads=16, dim=128, vdim=128), experts=16, top=4, ff=1024),
+    "small": dict(pool=8, right=dict(heads=16, dim=64, vdim=64), experts=8, top=4, ff=512),
+}
+
+
+def gerupel_config(name: str):
+    from .hybrid import HybridConfig
+
+    sz, gm = SIZES[name], GERUPEL_MIXERS[name]
+    a = sz["attn"]
+    band = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}
+    left = {"heads": a["heads"], "kv_heads": a["kv_heads"], "dim": a["dim"], "vdim": a["vdim"], "scale": a["dim"] ** -0.5,
+            "rot": {"dims": a["dim"] // 2, "base": 500000.0, "scaling": band}, "mask": {"size": a["window"], "pool": gm["pool"]}}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": dict(gm["right"]), "left_scale": 0.8, "right_scale": 1.1},
+             "mlp": {"kind": "moe", "router": {"experts": gm["experts"], "top": gm["top"], "scale": 2.0}, "expert": {"ff": gm["ff"]}}}
+    assert sz["layers"] == 8
+    return HybridConfig.from_dict({"architecture": "Gerupel", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-6},
+                                   "residual_mult": 0.5, "loop": {"start": 2, "stop": 4, "times": 2}, "layers": [layer] * 6})
+
+
+def _gerupel_floors(name, t, s_pre, ctx, b, prefill):
+    """Algorithmic (flops, bytes) per launch of the dual-norm parallel design's own kernels at `t` tokens."""
+    sz, gm = SIZES[name], GERUPEL_MIXERS[name]
+    a, r, w = sz["attn"], gm["right"], sz["width"]
+    h, g, d, dv, win, pool = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["window"], gm["pool"]
+    seen = lambda i: min(i + 1, win) + max(0, (i - win + 1) // pool)  # noqa: E731  keys and blocks that position i sees
+    if prefill:
+        pairs_qk = float(sum(seen(i) for i in range(s_pre)))
+        kv_rows = s_pre + s_pre // pool
+        nseq = 1
+    else:
+        pairs_qk = float(b * seen(ctx))
+        kv_rows = b * seen(ctx)
+        nseq = b
+    att = (2.0 * h * pairs_qk * (d + dv), 2.0 * kv_rows * g * (d + dv) + t * h * (4 * d + 2 * dv))
+    hd, hp = r["heads"] * r["dim"], r["heads"] * r["vdim"]
+    c = (h + g) * d + g * dv
+    npairs = t * gm["top"]
+    used = min(gm["experts"], npairs)
+    out = {k + "[pool]": att for k in ("swa_sink_attn_prefill", "swa_sink_attn", "swa_sink_attn_decode_tc")}
+    out.update({
+        "gated_scan": (6.0 * t * hd * r["vdim"], t * 4.0 * (2 * hd + 2 * hp) + 8.0 * nseq * hd * r["vdim"]),
+        "gated_scan_prep": (0.0, t * 16.0 * hd),
+        "head_rmsnorm_gate": (0.0, t * hp * 6.0),
+        "qk_norm_rope_kv_write": (0.0, t * (4.0 * c + 4.0 * h * d + 2.0 * g * (d + dv))),
+        "kv_pool_mean": (0.0, (t // pool + (0 if prefill else t)) * 2.0 * g * (d + dv) * (pool + 1)),
+        "scaled_add_rmsnorm2": (0.0, t * w * (4 + 4 + 4 + 4 + 4 * gm["top"] + 2 + 2.0)),
+        "embed_rmsnorm": (0.0, t * w * 6.0),
+        "moe_gate_up_glu": (4.0 * npairs * gm["ff"] * w, used * 4.0 * gm["ff"] * w + t * 2 * w + npairs * 2 * gm["ff"]),
+        "moe_down": (2.0 * npairs * gm["ff"] * w, used * 2.0 * gm["ff"] * w + npairs * (2 * gm["ff"] + 4 * w)),
+        "moe_gather_scale": (0.0, npairs * w * 4.0),
+    })
+    return out
 
 
 def zudarax_config(name: str):
@@ -210,7 +270,7 @@ def _floors(cfg, sz, t, keys_per_query, kv_tokens, nseq):
     att = (2.0 * t * a["heads"] * keys_per_query * (a["dim"] + a["vdim"]),
            2.0 * kv_tokens * a["kv_heads"] * (a["dim"] + a["vdim"]) + t * a["heads"] * (4 * a["dim"] + 2 * a["vdim"]))
     return {
-        "swa_sink_attn_prefill": att,
+        "swa_sink_attn_prefill": att, "swa_sink_attn_decode_tc": att,
         "swa_sink_attn": (2.0 * t * a["heads"] * keys_per_query * (a["dim"] + a["vdim"]),
                           2.0 * kv_tokens * a["kv_heads"] * (a["dim"] + a["vdim"]) + t * a["heads"] * (4 * a["dim"] + 2 * a["vdim"])),
         "ssd_scan": (6.0 * t * s["heads"] * s["state"] * s["vdim"],
@@ -291,13 +351,13 @@ def run(args):
     flush = torch.empty(192 << 20, dtype=torch.float32, device=dev)  # 768 MB > L2
     names = list(SIZES) if args.hybrid == "all" else [args.hybrid]
     for name in names:
-        kenetar, zudarax = name.startswith("kenetar-"), name.startswith("zudarax-")
-        short = name.split("-", 1)[1] if kenetar or zudarax else name
+        kenetar, zudarax, gerupel = name.startswith("kenetar-"), name.startswith("zudarax-"), name.startswith("gerupel-")
+        short = name.split("-", 1)[1] if kenetar or zudarax or gerupel else name
         sz = SIZES[short]
         cfg = hybrid_config(sz)
         s_pre, b, ctx = sz["prefill"], sz["batch"], sz["ctx"]
         bs = 32
-        res = {"metric": "kenetar_vs_pumopel_tokens_per_s" if kenetar else "zudarax_vs_dense_tokens_per_s" if zudarax else
+        res = {"metric": "gerupel_vs_pumopel_tokens_per_s" if gerupel else "kenetar_vs_pumopel_tokens_per_s" if kenetar else "zudarax_vs_dense_tokens_per_s" if zudarax else
                "hybrid_vs_dense_tokens_per_s", "size": name,
                "dtype": "bf16", "data": "synthetic (random weights)",
                "roofline_peaks": {"hbm_gbs": hbm / 1e9, "bf16_tflops": peak / 1e12, "source": src},
@@ -306,6 +366,13 @@ def run(args):
         win = sz["attn"]["window"]
         pum_floors = lambda t, pre: _floors(cfg, sz, t, min(win, s_pre / 2) if pre else min(win, ctx + 1),  # noqa: E731
                                             s_pre if pre else b * min(win, ctx + 1), 1 if pre else b)
+        if gerupel:
+            ger_floors = lambda t, pre: _gerupel_floors(short, t, s_pre, ctx, b, pre)  # noqa: E731
+            res["gerupel"] = _time_hybrid(gerupel_config(short), sz, args, ger_floors, flush, hbm, peak)[0]
+            res["pumopel"] = _time_hybrid(cfg, sz, args, pum_floors, flush, hbm, peak)[0]
+            res["gpu_launches"] = ops.launch_count()
+            print(json.dumps(res), flush=True)
+            continue
         if kenetar:
             ken_floors = lambda t, pre: _kenetar_floors(short, t, s_pre / 2 if pre else ctx + 1,  # noqa: E731
                                                         s_pre if pre else b * (ctx + 1), 1 if pre else b)
