@@ -493,9 +493,14 @@ int b200_gated_scan_prep(float* proj, int ld, int q_col0, int f_col0, int n, con
                          void* stream);
 /* Gated linear recurrence over a ragged batch: per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q, f [H][D]
  * and v [H][P] the columns q_col0 / f_col0 / v_col0 of the fp32 rows proj.  state fp32 [slots][H][P][D] (transposed), read for
- * sequences with seq_pos0 > 0 and written back for all; out fp32 [T][H * P].  D <= 512, else B200_ERR_UNSUPPORTED. */
+ * sequences with seq_pos0 > 0 and written back for all; out fp32 [T][H * P].  D <= 512, else B200_ERR_UNSUPPORTED.
+ * num_segs > 0: the step's portions cut into segments that run in parallel -- segs int32 [num_segs][4] = (first token, end token,
+ * sequence, 1 = first of its sequence | 2 = last), seq_seg0 int32 [B + 1] first segment per sequence, scratch seg_state fp32
+ * [num_segs][H][P][D] and seg_decay fp32 [num_segs][H][D]: a partial pass from zero states, an elementwise pass that chains
+ * the segments with the per-row products of f, and the full pass from every segment's start state. */
 int b200_gated_scan(const float* proj, int ld, int q_col0, int f_col0, int v_col0, float* state, const int32_t* seq_start,
-                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int D, int P, void* stream);
+                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int D, int P, const int32_t* segs,
+                    int num_segs, const int32_t* seq_seg0, float* seg_state, float* seg_decay, void* stream);
 /* gate_up fp32 [T][2 ff] (gate first): out = act(gate) * up, act = B200_ACT_SILU or B200_ACT_GELU_TANH */
 int b200_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, int act, void* stream);
 /* Gated delta rule, preparation: qkv fp32 rows [q: G*D | k: G*D | v: H*P] (pitch ldc) are the convolved activations; q and k

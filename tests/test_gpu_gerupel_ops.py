@@ -350,6 +350,44 @@ def test_gated_recurrence_over_portions_slots_and_reuse(H, D, P, lead):
     _close(o, want(fresh), 2e-5)
 
 
+@pytest.mark.parametrize("H,D,P,lead", [(2, 10, 7, 3), (2, 64, 48, 0), (1, 200, 20, 4)])
+def test_gated_recurrence_with_long_portions_cut_into_parallel_segments(H, D, P, lead):
+    """Portions of 256 tokens and more run as segments of 128 that are chained afterwards: a long portion from position 0, one
+    that continues a sequence (its first segment starts from the slot's state), a length that is no multiple of the segment, and
+    short portions of other sequences in the same step."""
+    from oracle.gerupel_ref import gated_recurrence
+
+    ops = _ops()
+    g = torch.Generator().manual_seed(D + P)
+    n = H * D
+    lens = {0: 1000, 1: 40, 3: 300}
+    lower, fb = 0.97 * torch.rand(n, generator=g), 0.5 * torch.randn(n, generator=g)
+    state = torch.full((5, H, P, D), 55.0, device=DEV)
+    width = lead + 2 * n + H * P + (2 if lead % 4 else 0)
+    pages = {0: list(range(1, 130)), 1: list(range(130, 140)), 3: list(range(140, 180))}
+    raws = {s: torch.randn(L, width, generator=g) * 1.5 for s, L in lens.items()}
+    steps = [{0: 333, 1: 2}, {0: 1, 1: 1, 3: 300}, {0: 410, 1: 37}, {0: 256}]
+    at, got = {s: 0 for s in lens}, {s: [] for s in lens}
+    for st in steps:
+        entries = [(s, at[s], c) for s, c in st.items()]
+        meta = _meta(entries, pages)
+        assert (meta.num_segs > 0) == (max(st.values()) >= 256)
+        rows = torch.cat([raws[s][at[s]:at[s] + c] for s, c in st.items()]).to(DEV)
+        o = ops.gated_scan(rows, lead, lead + n, lead + 2 * n, fb.to(DEV), lower.to(DEV), state, meta, H, D, P)
+        k = 0
+        for s, c in st.items():
+            got[s].append(o[k:k + c])
+            at[s] += c
+            k += c
+    for s, raw in raws.items():
+        r = raw.double()
+        q = torch.nn.functional.silu(r[:, lead:lead + n]).view(-1, H, D)
+        f = (lower.double() + (1 - lower.double()) * torch.sigmoid(r[:, lead + n:lead + 2 * n] + fb.double())).view(-1, H, D)
+        want = gated_recurrence(q, f, r[:, lead + 2 * n:lead + 2 * n + H * P].view(-1, H, P)).reshape(-1, H * P)
+        _close(torch.cat(got[s]), want, 2e-5)
+    assert (state[2] == 55.0).all() and (state[4] == 55.0).all()
+
+
 def test_gated_recurrence_keeps_a_long_memory():
     """Forget gates close to 1 (lower bound 0.999) over 1500 tokens in single-token steps after a prompt: what the first token wrote
     is still most of the state at the end, and 1 - f, tiny, is what every later token writes."""

@@ -113,7 +113,7 @@ SIGNATURES = {
     "b200_embed_rmsnorm": (_i, [_p, _p, _i, _p, _f, _p, _i, _i, _i, _p]),
     "b200_scaled_add_rmsnorm2": (_i, [_p, _p, _i, _f, _p, _i, _f, _p, _i, _p, _f, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _p]),
     "b200_gated_scan_prep": (_i, [_p, _i, _i, _i, _i, _p, _p, _i, _p]),
-    "b200_gated_scan": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "b200_gated_scan": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _p]),
     "b200_delta_prep": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p]),
     "b200_delta_scan": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "b200_latent_kv_write": (_i, [_p, _i, _i, _i, _i, _i, _p, _f, _p, _p, _p, _p, _p, _i, _i, _p]),

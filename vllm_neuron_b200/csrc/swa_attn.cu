@@ -294,16 +294,22 @@ __global__ void __launch_bounds__(PM_THREADS)
         po[threadIdx.x] = p % bs;
       }
       __syncthreads();
-#pragma unroll 4
-      for (int k = 0; k < np; ++k) {
-        const int64_t blk = pg[k];
-        const int o = po[k];
+      // eight rows of a column in flight at a time (the index is clamped, so every load is unconditional); summed in order
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (width[u]) {
-            const int N = src[u] == k_pool ? G : Gv;
-            acc[u] += ldf(src[u], (blk * N * bs + o) * width[u] + off[u]);
+      for (int u = 0; u < 8; ++u) {
+        if (!width[u]) continue;
+        const int64_t per_page = (int64_t)(src[u] == k_pool ? G : Gv) * bs;
+        for (int k0 = 0; k0 < np; k0 += 8) {
+          float v[8];
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const int k = k0 + kk < np ? k0 + kk : np - 1;
+            v[kk] = ldf(src[u], (pg[k] * per_page + po[k]) * width[u] + off[u]);
           }
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            if (k0 + kk < np) acc[u] += v[kk];
+        }
       }
     }
 #pragma unroll

@@ -1198,10 +1198,16 @@ def kv_pool_mean(k_pool, v_pool, pk_pool, pv_pool, block_table, meta, pool: int)
                                              meta.num_tokens, g, gv, d, dv, bs, int(pool), _stream()), "b200_kv_pool_mean")
 
 
+_GATED_SEGS = {"0": False, "1": True}.get(os.environ.get("B200_GATED_SEGS", ""))
+GATED_SEGS_MAX_CTAS = 600  # whole-portion CTAs (16 value columns x head x sequence; about four per SM) below which long portions run as segments
+
+
 def gated_scan(proj, q_col0: int, f_col0: int, v_col0: int, f_bias, lower, state, meta, heads: int, dim: int, vdim: int):
     """Gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T q per head over a ragged batch.  Raw q / f / v are the columns
     q_col0 / f_col0 / v_col0 of the fp32 rows proj; q = silu(raw), f = lower + (1 - lower) sigmoid(raw + f_bias) are written back
-    IN PLACE.  state fp32 [slots, H, vdim, dim] (transposed) updated in place; returns o fp32 [T, H * vdim]."""
+    IN PLACE.  state fp32 [slots, H, vdim, dim] (transposed) updated in place; returns o fp32 [T, H * vdim].  When the step
+    carries a segment list (meta.scan_segs: some portion is long) the segments run in parallel from start states that an
+    elementwise pass chains together."""
     _cuda(proj, f_bias, lower, state)
     _f32(f_bias, lower, state)
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.shape[1:] == (heads, vdim, dim)
@@ -1212,8 +1218,19 @@ def gated_scan(proj, q_col0: int, f_col0: int, v_col0: int, f_bias, lower, state
     with _k("gated_scan_prep"):
         check(lib.b200_gated_scan_prep(_ptr(proj), proj.stride(0), q_col0, f_col0, heads * dim, _ptr(f_bias), _ptr(lower), t,
                                        _stream()), "b200_gated_scan_prep")
+    segs = getattr(meta, "scan_segs", None)
+    nseg = meta.num_segs if segs is not None else 0
+    if _GATED_SEGS is not None:  # A/B aid: B200_GATED_SEGS=0 never cuts portions, =1 always does when the step has a list
+        nseg = nseg if _GATED_SEGS else 0
+    elif -(-vdim // 16) * heads * meta.num_seqs >= GATED_SEGS_MAX_CTAS:
+        nseg = 0  # whole portions already give every SM its CTAs: the two passes of the segment scheme would only add work
+    seg_state = seg_decay = None
+    if nseg:
+        seg_state = torch.empty((nseg, heads, vdim, dim), dtype=torch.float32, device=proj.device)
+        seg_decay = torch.empty((nseg, heads, dim), dtype=torch.float32, device=proj.device)
     with _k("gated_scan"):
         check(lib.b200_gated_scan(_ptr(proj), proj.stride(0), q_col0, f_col0, v_col0, _ptr(state), _ptr(meta.seq_start),
-                                  _ptr(meta.seq_slot), _ptr(meta.seq_pos0), _ptr(out), meta.num_seqs, heads, dim, vdim, _stream()),
-              "b200_gated_scan")
+                                  _ptr(meta.seq_slot), _ptr(meta.seq_pos0), _ptr(out), meta.num_seqs, heads, dim, vdim,
+                                  _ptr(segs) if nseg else 0, nseg, _ptr(meta.scan_seq_seg0) if nseg else 0, _ptr(seg_state),
+                                  _ptr(seg_decay), _stream()), "b200_gated_scan")
     return out
