@@ -356,14 +356,15 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
                        int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, int chunk,
                        float softcap, const float* sigmoid_bias, int v_div, int out_f32, int splits, float* split_workspace,
                        const void* pooled_k, const void* pooled_v, int pool, void* stream);
-/* Means of the key / value blocks that the step completes: for every token t of the step whose position closes a block of `pool`
- * positions (tok_pos[t] % pool == pool - 1; slot_mapping[t] >= 0) the block's `pool` key and value rows are read back from the
- * pools through block-table row tok_row[t], summed in fp32, divided by `pool` and written to
+/* Means of the key / value blocks that the step completes: sequence s brings tokens [seq_start[s], seq_start[s+1]) at positions
+ * seq_pos0[s].. (block-table row seq_slot[s]); for every block of `pool` positions whose last position is among them the block's
+ * `pool` key and value rows are read back from the pools, summed in fp32, divided by `pool` and written to
  * pooled_k [num_blocks][G][ppb][D] / pooled_v [num_blocks][Gv][ppb][Dv], ppb = ceil(block_size / pool): the entry of a block lives
- * in the page of the block's last position e, at index (e % block_size) / pool.  Run it after the step's keys are written. */
+ * in the page of the block's last position e, at index (e % block_size) / pool.  T = tokens of the step (sizes the launch).
+ * Run it after the step's keys are written. */
 int b200_kv_pool_mean(const void* k_pool, const void* v_pool, void* pooled_k, void* pooled_v, int kv_dtype,
-                      const int32_t* block_table, int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos,
-                      const int64_t* slot_mapping, int T, int G, int Gv, int D, int Dv, int block_size, int pool, void* stream);
+                      const int32_t* block_table, int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot,
+                      const int32_t* seq_pos0, int B, int T, int G, int Gv, int D, int Dv, int block_size, int pool, void* stream);
 /* The same attention for prompt portions on the tensor cores (bf16 pools; D and Dv multiples of 16, Dv <= 256, else
  * B200_ERR_UNSUPPORTED): sequence s brings tokens [seq_start[s], seq_start[s+1]) at positions seq_pos0[s].., block-table row
  * seq_slot[s]; max_new = the longest portion of the step.  q is rounded to bf16; softmax and accumulation are fp32.

@@ -17,12 +17,12 @@ def _layer(mask=None, mlp=True, scaling=None, **left):
         lm["rot"] = {**lm["rot"], "scaling": scaling}
     if mask:
         lm["mask"] = mask
-    return {"type": "parallel", "mixer": {"left": lm, "right": {"heads": 3, "dim": 7, "vdim": 4}, "left_scale": 0.8, "right_scale": 1.25},
+    return {"type": "parallel", "mixer": {"left": lm, "right": {"heads": 3, "dim": 7, "vdim": 4}, "left_scale": 0.7, "right_scale": 1.25},
             "mlp": {"kind": "moe", "router": {"experts": 5, "top": 2, "scale": 1.5}, "expert": {"ff": 9}} if mlp else None}
 
 
 def _cfg(layers=None, loop=None):
-    band = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 16}
+    band = {"factor": 5.0, "low": 1.0, "high": 3.0, "original": 16}
     d = {"architecture": "Gerupel", "vocab": 20, "width": 12, "norm": {"eps": 1e-5}, "residual_mult": 0.6,
          "layers": layers if layers is not None else [_layer({"size": 9, "pool": 4}, scaling=band), _layer({"size": 5}, mlp=False),
                                                       _layer(None)]}
@@ -40,7 +40,7 @@ def test_config_reader_round_trip_and_shapes():
     assert all(isinstance(m, DualMixerSpec) and isinstance(m.left, RotAttnSpec) and isinstance(m.right, GatedScanSpec) for m in (m0, m1, m2))
     assert (m0.left.window, m0.left.pool, m1.left.window, m1.left.pool, m2.left.window, m2.left.pool) == (9, 4, 5, 0, 0, 0)
     assert m0.left.unit_sink and m0.left.temp and m0.left.rot.half and m0.left.rot.scaling["low"] == 1.0 and m1.left.rot.scaling is None
-    assert (m0.left_scale, m0.right_scale) == (0.8, 1.25) and (m0.right.heads, m0.right.dim, m0.right.vdim) == (3, 7, 4)
+    assert (m0.left_scale, m0.right_scale) == (0.7, 1.25) and (m0.right.heads, m0.right.dim, m0.right.vdim) == (3, 7, 4)
     f = cfg.layers[0].mlp
     assert isinstance(f, MoeSpec) and (f.experts, f.top, f.ff, f.route, f.scale) == (5, 2, 9, "softmax_renorm", 1.5)
     assert cfg.layers[1].mlp is None

@@ -186,7 +186,7 @@ def _cuts(T):
 
 
 @pytest.mark.parametrize("kv_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,pool,bs", [(9, 4, 8), (16, 8, 8), (5, 8, 8), (40, 3, 8), (1, 1, 8), (33, 20, 8), (24, 16, 32)])
+@pytest.mark.parametrize("window,pool,bs", [(9, 4, 8), (16, 8, 8), (5, 8, 8), (44, 3, 8), (1, 1, 8), (33, 20, 8), (24, 16, 32)])
 def test_block_means_are_the_means_of_the_cached_rows(kv_dtype, window, pool, bs):
     """Blocks that divide the page, straddle pages and exceed a page; closed inside a portion, by a portion's first token and by a
     single decoded token.  Every closed block's row is where the attention kernels look for it; no other row is touched."""
@@ -207,7 +207,7 @@ def test_block_means_are_the_means_of_the_cached_rows(kv_dtype, window, pool, bs
 
 
 @pytest.mark.parametrize("kv_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,pool", [(9, 4), (16, 8), (5, 8), (40, 3), (1, 1), (33, 20), (64, 32), (7, 0)])
+@pytest.mark.parametrize("window,pool", [(9, 4), (16, 8), (5, 8), (44, 3), (1, 1), (33, 20), (64, 32), (7, 0)])
 def test_window_with_pooled_blocks_at_every_edge(kv_dtype, window, pool):
     """Loud keys (eight times the others) sit on both sides of the window's edge of late queries and fill whole blocks, so a
     window that is one position off, a block that is seen one position early or late, or a block that is lost moves the output
@@ -308,7 +308,7 @@ def test_unequal_sequences_in_one_step_see_their_own_blocks(kv_dtype):
 
 
 # ------------------------------------------------------------------------------------------------ gated linear recurrence
-@pytest.mark.parametrize("H,D,P,lead", [(2, 10, 7, 3), (3, 48, 64, 0), (1, 33, 20, 1), (2, 128, 32, 4), (1, 256, 16, 8), (4, 4, 5, 0), (1, 500, 3, 0)])
+@pytest.mark.parametrize("H,D,P,lead", [(2, 10, 7, 3), (3, 40, 72, 0), (1, 33, 20, 1), (2, 128, 32, 4), (1, 256, 16, 8), (4, 4, 5, 0), (1, 500, 3, 0)])
 def test_gated_recurrence_over_portions_slots_and_reuse(H, D, P, lead):
     """Raw projections -> silu / bounded forget gate -> recurrence, for a sequence cut into portions beside another sequence in the
     same steps; then the first sequence's slot is taken over by a new one, which must not see the old state."""
@@ -412,7 +412,7 @@ def test_gated_recurrence_keeps_a_long_memory():
 
 
 # ------------------------------------------------------------------------------------------------ router
-@pytest.mark.parametrize("E,top", [(16, 4), (5, 1), (3, 3), (1, 1), (64, 8)])
+@pytest.mark.parametrize("E,top", [(12, 3), (5, 1), (3, 3), (1, 1), (64, 8)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_renormalised_softmax_router_and_experts(E, top, dtype):
     """Scores over all experts, the largest kept and divided by their sum; the experts' outputs weighed in the residual step."""
@@ -420,7 +420,7 @@ def test_renormalised_softmax_router_and_experts(E, top, dtype):
 
     ops = _ops()
     g = torch.Generator().manual_seed(E + top)
-    T, W, ff, scale = 40, 64, 32, 2.5
+    T, W, ff, scale = 40, 64, 32, 1.7
     h = _bf16_values(T, W, g=g)
     Wt = {"router": _bf16_values(E, W, g=g, scale=0.6)}
     for e in range(E):

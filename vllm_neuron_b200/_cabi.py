@@ -82,7 +82,7 @@ SIGNATURES = {
     "b200_causal_conv": (_i, [_p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "b200_swa_sink_attn": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _i,
                                 _i, _p, _p, _p, _i, _p]),
-    "b200_kv_pool_mean": (_i, [_p, _p, _p, _p, _i, _p, _i64, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_kv_pool_mean": (_i, [_p, _p, _p, _p, _i, _p, _i64, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _f,
                                         _p, _i, _i, _i, _p, _p, _i, _p]),
     "b200_swa_sink_attn_prefill_tc_supported": (_i, [_i, _i, _i, _i, _i, _i]),

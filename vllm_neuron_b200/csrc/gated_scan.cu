@@ -273,10 +273,23 @@ __global__ void gated_seg_combine_kernel(const float* __restrict__ state, float*
     const int h = (int)(e / ((int64_t)P * D)), i = (int)(e % D);
     const int s0 = seq_seg0[sq], s1 = seq_seg0[sq + 1];
     float carry = seq_pos0[sq] > 0 ? state[(int64_t)seq_slot[sq] * per_seq + e] : 0.f;
-    for (int k = s0; k < s1; ++k) {
-      const float z = seg_state[(int64_t)k * per_seq + e];
-      seg_state[(int64_t)k * per_seq + e] = carry;
-      if (k + 1 < s1) carry = fmaf(seg_decay[((int64_t)k * H + h) * D + i], carry, z);
+    // eight segments' loads are issued before the first store (the stores go to the array the loads read: without the batch
+    // every load would wait for the store before it)
+    for (int k0 = s0; k0 < s1; k0 += 8) {
+      float z[8], a[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + u < s1 ? k0 + u : s1 - 1;
+        z[u] = seg_state[(int64_t)k * per_seq + e];
+        a[u] = seg_decay[((int64_t)k * H + h) * D + i];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (k0 + u < s1) {
+          seg_state[(int64_t)(k0 + u) * per_seq + e] = carry;
+          if (k0 + u + 1 < s1) carry = fmaf(a[u], carry, z[u]);
+        }
+      }
     }
   }
 }

@@ -241,9 +241,10 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const float* __restrict__ src, 
   }
 }
 
-// Block means for attention that sees far-away blocks of `pool` positions as one key / value each.  One CTA per token of the
-// step; the CTA of a token that CLOSES a block (position = b pool + pool - 1) reads the block's `pool` key and value rows back
-// from the pools through the sequence's block table (rows of earlier steps and of this one alike: what is averaged is what
+// Block means for attention that sees far-away blocks of `pool` positions as one key / value each.  One CTA per block that the
+// step CLOSES (a portion at positions [p0, p0 + n) closes (p0 + n) / pool - p0 / pool blocks; the launch has T / pool + B CTAs,
+// an upper bound, and CTA i finds its (sequence, block) by walking the step's sequences); it reads the block's `pool` key and
+// value rows back from the pools through the sequence's block table (rows of earlier steps and of this one alike: what is averaged is what
 // the cache holds), sums them in fp32, divides by `pool` and writes the mean into the pooled pools
 // PK [num_blocks][G][ppb][D], PV [num_blocks][Gv][ppb][Dv], ppb = ceil(block_size / pool): the entry of block b lives in the page
 // that holds the block's last position e, at index (e % block_size) / pool.  Runs after the step's keys and values are written.
@@ -254,15 +255,24 @@ template <typename KT>
 __global__ void __launch_bounds__(PM_THREADS)
     kv_pool_mean_kernel(const KT* __restrict__ k_pool, const KT* __restrict__ v_pool, KT* __restrict__ pk_pool,
                         KT* __restrict__ pv_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
-                        const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos,
-                        const int64_t* __restrict__ slots, int G, int Gv, int D, int Dv, int bs, int pool, int ppb) {
+                        const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
+                        const int32_t* __restrict__ seq_pos0, int B, int G, int Gv, int D, int Dv, int bs, int pool, int ppb) {
   griddep_launch();
   griddep_wait();
   __shared__ int32_t pg[PM_ROWS], po[PM_ROWS];  // page and offset in the page of the round's positions
-  const int t = blockIdx.x;
-  const int pos = tok_pos[t];
-  if (slots[t] < 0 || (pos + 1) % pool != 0) return;
-  const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
+  int sq = -1, pos = 0;
+  for (int s = 0, acc = 0; s < B; ++s) {  // the same walk in every thread
+    const int p0 = seq_pos0[s], n = seq_start[s + 1] - seq_start[s];
+    const int cnt = (p0 + n) / pool - p0 / pool;
+    if ((int)blockIdx.x < acc + cnt) {
+      sq = s;
+      pos = (p0 / pool + ((int)blockIdx.x - acc)) * pool + pool - 1;  // the block's last position
+      break;
+    }
+    acc += cnt;
+  }
+  if (sq < 0) return;
+  const int32_t* bt = block_table + (int64_t)seq_slot[sq] * bt_stride;
   const int first = pos - pool + 1;
   const int64_t dst_blk = bt[pos / bs];
   const int dst_idx = (pos % bs) / pool;
@@ -638,16 +648,16 @@ int b200_qk_norm_rope_kv_write(const float* src, int ld, int q_col0, int k_col0,
 }
 
 int b200_kv_pool_mean(const void* k_pool, const void* v_pool, void* pooled_k, void* pooled_v, int kv_dtype,
-                      const int32_t* block_table, int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos,
-                      const int64_t* slot_mapping, int T, int G, int Gv, int D, int Dv, int block_size, int pool, void* stream) {
-  B200_REQUIRE(k_pool && v_pool && pooled_k && pooled_v && block_table && tok_row && tok_pos && slot_mapping, "kv_pool_mean: null pointer");
+                      const int32_t* block_table, int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot,
+                      const int32_t* seq_pos0, int B, int T, int G, int Gv, int D, int Dv, int block_size, int pool, void* stream) {
+  B200_REQUIRE(k_pool && v_pool && pooled_k && pooled_v && block_table && seq_start && seq_slot && seq_pos0, "kv_pool_mean: null pointer");
   B200_REQUIRE(pool >= 1 && G >= 1 && Gv >= 1 && D >= 1 && Dv >= 1 && block_size >= 1, "kv_pool_mean: blocks of %d positions", pool);
-  if (T <= 0) return B200_OK;
+  if (T <= 0 || B <= 0) return B200_OK;
   const int ppb = (block_size + pool - 1) / pool;
   B200_DISPATCH_ELEM(kv_dtype, KT,
-                     B200_CUDA_OK(launch_kernel(kv_pool_mean_kernel<KT>, dim3(T), dim3(PM_THREADS), 0, (cudaStream_t)stream, (const KT*)k_pool,
-                                                (const KT*)v_pool, (KT*)pooled_k, (KT*)pooled_v, block_table, bt_stride, tok_row,
-                                                tok_pos, slot_mapping, G, Gv, D, Dv, block_size, pool, ppb)));
+                     B200_CUDA_OK(launch_kernel(kv_pool_mean_kernel<KT>, dim3(T / pool + B), dim3(PM_THREADS), 0, (cudaStream_t)stream,
+                                                (const KT*)k_pool, (const KT*)v_pool, (KT*)pooled_k, (KT*)pooled_v, block_table,
+                                                bt_stride, seq_start, seq_slot, seq_pos0, B, G, Gv, D, Dv, block_size, pool, ppb)));
   return B200_OK;
 }
 

@@ -69,11 +69,11 @@ def gerupel_config(name: str):
     band = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}
     left = {"heads": a["heads"], "kv_heads": a["kv_heads"], "dim": a["dim"], "vdim": a["vdim"], "scale": a["dim"] ** -0.5,
             "rot": {"dims": a["dim"] // 2, "base": 500000.0, "scaling": band}, "mask": {"size": a["window"], "pool": gm["pool"]}}
-    layer = {"type": "parallel", "mixer": {"left": left, "right": dict(gm["right"]), "left_scale": 0.8, "right_scale": 1.1},
+    layer = {"type": "parallel", "mixer": {"left": left, "right": dict(gm["right"]), "left_scale": 0.9, "right_scale": 1.2},
              "mlp": {"kind": "moe", "router": {"experts": gm["experts"], "top": gm["top"], "scale": 2.0}, "expert": {"ff": gm["ff"]}}}
     assert sz["layers"] == 8
     return HybridConfig.from_dict({"architecture": "Gerupel", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-6},
-                                   "residual_mult": 0.5, "loop": {"start": 2, "stop": 4, "times": 2}, "layers": [layer] * 6})
+                                   "residual_mult": 0.6, "loop": {"start": 2, "stop": 4, "times": 2}, "layers": [layer] * 6})
 
 
 def _gerupel_floors(name, t, s_pre, ctx, b, prefill):

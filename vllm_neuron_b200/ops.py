@@ -1183,7 +1183,7 @@ def scaled_add_rmsnorm2(x, eps: float, *, y1=None, c1: float = 1.0, y2=None, c2:
 
 
 def kv_pool_mean(k_pool, v_pool, pk_pool, pv_pool, block_table, meta, pool: int):
-    """For every token of the step that closes a block of `pool` positions: the mean of the block's cached key rows and value rows
+    """For every block of `pool` positions that the step's portions close: the mean of the block's cached key rows and value rows
     -> the pooled pools [num_blocks, G, ceil(block_size / pool), D | Dv] (entry of a block: page of its last position)."""
     _cuda(k_pool, v_pool, pk_pool, pv_pool, block_table)
     _, g, bs, d = k_pool.shape
@@ -1194,8 +1194,9 @@ def kv_pool_mean(k_pool, v_pool, pk_pool, pv_pool, block_table, meta, pool: int)
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     with _k("kv_pool_mean"):
         check(_cabi.load().b200_kv_pool_mean(_ptr(k_pool), _ptr(v_pool), _ptr(pk_pool), _ptr(pv_pool), _edt(k_pool), _ptr(block_table),
-                                             block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos), _ptr(meta.slot_mapping),
-                                             meta.num_tokens, g, gv, d, dv, bs, int(pool), _stream()), "b200_kv_pool_mean")
+                                             block_table.stride(0), _ptr(meta.seq_start), _ptr(meta.seq_slot), _ptr(meta.seq_pos0),
+                                             meta.num_seqs, meta.num_tokens, g, gv, d, dv, bs, int(pool), _stream()),
+              "b200_kv_pool_mean")
 
 
 _GATED_SEGS = {"0": False, "1": True}.get(os.environ.get("B200_GATED_SEGS", ""))
